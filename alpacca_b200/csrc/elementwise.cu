@@ -1,0 +1,241 @@
+// Memory-bound kernels around the matrix products: embedding gather, fused
+// residual add + RMSNorm, rotation of q and k with the append of k and v to the
+// paged cache, SwiGLU on the fused gate|up product, bias add.
+//
+// Arithmetic is 32-bit throughout (sums of squares, scaling, rotation, SiLU);
+// T is the storage type of activations, weights and cache (float or bfloat16).
+// The residual stream itself is always float.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// x[t,:] = table[token[t],:]   (alpacca/model.py:482; no scaling)
+// Tokens outside the table give a row of NaN, never a read outside it.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                  float* __restrict__ out, int n_rows, int width, int vocab) {
+  const int row = blockIdx.x;
+  if (row >= n_rows) return;
+  const int tok = tokens[row];
+  float* o = out + (size_t)row * width;
+  if (tok < 0 || tok >= vocab) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const T* src = table + (size_t)tok * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(src[i]);
+}
+
+AB_API int ab_embed_rows(const void* table, int dtype, const int* tokens, float* out, int n_rows,
+                         int width, int vocab, cudaStream_t stream) {
+  if (n_rows <= 0) return AB_OK;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == AB_F32)
+    embed_rows_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, tokens, out, n_rows, width, vocab);
+  else if (dtype == AB_BF16)
+    embed_rows_kernel<bf16><<<n_rows, threads, 0, stream>>>((const bf16*)table, tokens, out, n_rows, width, vocab);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Fused residual add + RMSNorm (alpacca/tensor.py:163-173):
+//   r = residual[src] (+ delta[src]);  residual[src] = r  (when delta is given and
+//   rows == nullptr);  inv = 1/sqrt(mean(r^2) + eps);  out[i] = (r * inv) * w.
+// `rows` picks source rows (the final norm runs on the wanted rows only); with
+// `rows` the residual is left as it is.  One block per output row; the order
+// of the sum depends on the width and the block size only.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows, int n_out, int width, float eps) {
+  __shared__ float scratch[32];
+  const int i_out = blockIdx.x;
+  if (i_out >= n_out) return;
+  const int src = rows ? rows[i_out] : i_out;
+  float* r = residual + (size_t)src * width;
+  const T* d = delta ? delta + (size_t)src * width : nullptr;
+  const bool write_back = (d != nullptr) && (rows == nullptr);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = r[i];
+    if (d) {
+      v += to_f32(d[i]);
+      if (write_back) r[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  if (out == nullptr) return;
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  T* o = out + (size_t)i_out * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = r[i];
+    if (d && !write_back) v += to_f32(d[i]);
+    o[i] = from_f32<T>((v * inv) * weight[i]);
+  }
+}
+
+AB_API int ab_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, int dtype,
+                          const int* rows, int n_out, int width, float eps, cudaStream_t stream) {
+  if (n_out <= 0) return AB_OK;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  if (dtype == AB_F32)
+    add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(residual, (const float*)delta, weight, (float*)out,
+                                                             rows, n_out, width, eps);
+  else if (dtype == AB_BF16)
+    add_rmsnorm_kernel<bf16><<<n_out, threads, 0, stream>>>(residual, (const bf16*)delta, weight, (bf16*)out,
+                                                            rows, n_out, width, eps);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// y[t, j] += bias[j]
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, size_t total, int width) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  y[i] = from_f32<T>(to_f32(y[i]) + bias[i % width]);
+}
+
+AB_API int ab_add_bias(void* y, int dtype, const float* bias, int n_rows, int width, cudaStream_t stream) {
+  size_t total = (size_t)n_rows * width;
+  if (total == 0) return AB_OK;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == AB_F32)
+    add_bias_kernel<float><<<blocks, 256, 0, stream>>>((float*)y, bias, total, width);
+  else if (dtype == AB_BF16)
+    add_bias_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)y, bias, total, width);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Rotation of q and k by position, and append of k and v to the paged cache.
+//
+// qkv: [n_tokens, (H + 2K) * D], q heads first, then k heads, then v heads.
+// Rotation (alpacca/model.py:381-435): pair (a, b) of a head, angle from the
+// table row of the token's position: out_a = x_a*c - x_b*s, out_b = x_a*s + x_b*c.
+// pairing 0 ("llama"): (2i, 2i+1); pairing 1 ("neox"): (i, n_rot/2 + i);
+// dims >= n_rot pass through.  cos/sin == nullptr: no rotation at all.
+// q is rotated in place; rotated k and plain v go to the cache (written before
+// attention so that a token sees itself, alpacca/model.py:501-503).
+// Cache pages: [n_pages][K][page_size][D]; the page of position p of sequence b
+// is block_table[b * table_width + p / page_size].  Tokens whose tok_seq is
+// negative are padding and are skipped.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_append_kernel(T* __restrict__ qkv, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                   int table_width, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                   int n_tokens, int H, int K, int D, int n_rot, int pairing, int page_size,
+                                   int write_cache) {
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const int b = tok_seq[t];
+  if (b < 0) return;
+  const int pos = tok_pos[t];
+  const int half_d = D >> 1, half_r = n_rot >> 1;
+  const int n_heads = H + 2 * K;
+  T* row = qkv + (size_t)t * n_heads * D;
+  const float* c_row = cos_t ? cos_t + (size_t)pos * half_r : nullptr;
+  const float* s_row = sin_t ? sin_t + (size_t)pos * half_r : nullptr;
+  const int page = block_table[(size_t)b * table_width + pos / page_size];
+  const int off = pos % page_size;
+  const int units = n_heads * half_d;
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    const int head = u / half_d, i = u - head * half_d;
+    T* x = row + (size_t)head * D;
+    int a, bb;
+    float xa, xb;
+    if (head < H + K && c_row && i < half_r) {
+      if (pairing == 0) { a = 2 * i; bb = a + 1; } else { a = i; bb = half_r + i; }
+      const float c = c_row[i], s = s_row[i];
+      const float x0 = to_f32(x[a]), x1 = to_f32(x[bb]);
+      xa = x0 * c - x1 * s;
+      xb = x0 * s + x1 * c;
+    } else {
+      // pass-through dims (and every dim of v): unit i covers two dims of its own
+      if (head < H + K && c_row) { a = n_rot + 2 * (i - half_r); } else { a = 2 * i; }
+      bb = a + 1;
+      xa = to_f32(x[a]);
+      xb = to_f32(x[bb]);
+    }
+    if (head < H) {
+      x[a] = from_f32<T>(xa);
+      x[bb] = from_f32<T>(xb);
+    } else if (write_cache) {
+      const bool is_k = head < H + K;
+      const int kh = is_k ? head - H : head - H - K;
+      T* dst = (is_k ? k_pages : v_pages) + (((size_t)page * K + kh) * page_size + off) * D;
+      dst[a] = from_f32<T>(xa);
+      dst[bb] = from_f32<T>(xb);
+      if (is_k) {  // keep the rotated k in the step's buffer too (parts that read it there)
+        x[a] = from_f32<T>(xa);
+        x[bb] = from_f32<T>(xb);
+      }
+    }
+  }
+}
+
+AB_API int ab_rope_append(void* qkv, int dtype, const float* cos_t, const float* sin_t, const int* tok_pos,
+                          const int* tok_seq, const int* block_table, int table_width, void* k_pages,
+                          void* v_pages, int n_tokens, int H, int K, int D, int n_rot, int pairing,
+                          int page_size, int write_cache, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if ((D & 1) || (n_rot & 1) || n_rot > D || n_rot < 0) return AB_BAD_ARG;
+  const int units = (H + 2 * K) * (D / 2);
+  const int threads = units >= 1024 ? 256 : 128;
+  if (dtype == AB_F32)
+    rope_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        (float*)qkv, cos_t, sin_t, tok_pos, tok_seq, block_table, table_width, (float*)k_pages, (float*)v_pages,
+        n_tokens, H, K, D, n_rot, pairing, page_size, write_cache);
+  else if (dtype == AB_BF16)
+    rope_append_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
+        (bf16*)qkv, cos_t, sin_t, tok_pos, tok_seq, block_table, table_width, (bf16*)k_pages, (bf16*)v_pages,
+        n_tokens, H, K, D, n_rot, pairing, page_size, write_cache);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU on the fused product gu = h @ [gate|up]^T (alpacca/model.py:513):
+//   act[t, j] = g / (1 + exp(-g)) * u
+// The fused matrix interleaves gate and up in groups of 8 rows: columns
+// 16*q + r hold gate 8*q + r, columns 16*q + 8 + r hold up 8*q + r (r < 8), which
+// is the order in which the skinny-matrix kernel's accumulators meet them.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, size_t total, int F) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / F;
+  const int j = (int)(idx - t * F);
+  const T* row = gu + t * (size_t)(2 * F);
+  const int q = j >> 3, r = j & 7;
+  const float g = to_f32(row[16 * q + r]);
+  const float u = to_f32(row[16 * q + 8 + r]);
+  act[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+AB_API int ab_swiglu(const void* gu, void* act, int dtype, int n_rows, int F, cudaStream_t stream) {
+  size_t total = (size_t)n_rows * F;
+  if (total == 0) return AB_OK;
+  if (F % 8) return AB_BAD_ARG;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == AB_F32)
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)act, total, F);
+  else if (dtype == AB_BF16)
+    swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)act, total, F);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}

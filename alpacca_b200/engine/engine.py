@@ -1,0 +1,80 @@
+"""The engine: a model, its cache, and the one step function.
+
+`Engine.step(entries)` runs exactly the tokens it is given, on top of what the
+slots hold, as one batch, and returns the logits at the wanted places.  Prompts
+of unequal lengths go in one step; afterwards one token per sequence.  The
+reference's counterparts are `prefill` / `forward_batch` / `forward`
+(alpacca/model.py:610-641, :469-518, :439-445), for its single sequence.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheFull, SequenceCache
+from ..parts.base import BuildOptions
+from .model import DecoderModel
+from .step import ContextBuilder, StepContext, StepEntry
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, max_tokens: int, max_slots: int | None = None,
+                 max_positions: int | None = None):
+        self.model = model
+        opts: BuildOptions = model.opts
+        self.device = torch.device(opts.device)
+        self.max_positions = int(max_positions or opts.max_positions)
+        n_pages = -(-int(max_tokens) // 64)
+        self.max_slots = int(max_slots) if max_slots else max(1, min(n_pages, 1024))
+        self.cache = SequenceCache(model.cache_entry_specs(), max_tokens, self.max_slots, self.max_positions,
+                                   opts.dtype, self.device)
+        self.vocab_size = model.spec.vocab_size
+        self._builder = ContextBuilder(self.device)
+
+    # -- slots -------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # -- the step ------------------------------------------------------------
+    def _check(self, entries) -> None:
+        if not entries:
+            raise ValueError("a step needs at least one sequence")
+        seen = set()
+        for e in entries:
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if not e.tokens:
+                raise ValueError(f"slot {e.slot}: a step needs at least one token per sequence")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise ValueError(f"token id {t} lies outside the vocabulary of {self.vocab_size}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise ValueError(f"slot {e.slot}: wanted place {w} is not among its {len(e.tokens)} tokens")
+
+    def prepare(self, entries) -> StepContext:
+        self._check(entries)
+        requests = [(e.slot, len(e.tokens)) for e in entries]
+        self.cache.reserve(requests)          # raises CacheFull before anything is launched
+        lengths = [self.cache.length(e.slot) for e in entries]
+        return self._builder.build(entries, lengths, self.cache)
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """Runs one step; returns float32 logits [number of wanted places, vocab] on the device,
+        in the order of the entries and of their `want` lists."""
+        ctx = self.prepare(entries)
+        logits = self.model.forward(ctx, self.cache)
+        self.cache.commit([(e.slot, len(e.tokens)) for e in entries])
+        return logits
+
+    def describe(self) -> str:
+        return self.cache.describe()
+
+
+__all__ = ["Engine", "StepEntry", "CacheFull"]

@@ -1,0 +1,110 @@
+"""A decoder as data: its parts and the order in which they run.
+
+`DecoderSpec` is what an architecture's build function returns: the embedding,
+the layers (each a block of parts), the schedule, the final norm and the head.
+The schedule is a list of runs; a run names the layer it executes and the cache
+entry it uses.  Naming a layer in two runs executes it twice (each run with a
+cache entry of its own); a run whose `reads_entry_of` names an earlier run
+attends to that run's cache and writes none.
+
+`DecoderModel` executes a spec for one step: embed the step's tokens, run the
+schedule, norm the wanted rows, project them to logits
+(alpacca/model.py:469-518 is the reference's form of the same pass).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..parts.base import BuildOptions, Norm, Part, PositionEncoding
+from ..parts.block import HiddenStream
+from ..parts.embedding import TokenEmbedding, VocabHead
+from ..weights.loader import Fetcher, check_names
+
+
+@dataclass(frozen=True)
+class Run:
+    layer: int                       # index into DecoderSpec.layers
+    reads_entry_of: int | None = None  # index of an earlier run whose cache this run reads
+
+
+@dataclass
+class DecoderSpec:
+    embedding: TokenEmbedding
+    layers: list                     # blocks: forward(stream, ctx, cache, write_cache)
+    final_norm: Norm
+    head: VocabHead
+    schedule: list[Run] = field(default_factory=list)
+    position: PositionEncoding | None = None   # an encoding that adds to the embeddings, if any
+    stop_token_ids: tuple = ()
+    vocab_size: int = 0
+
+    def __post_init__(self):
+        if not self.schedule:
+            self.schedule = [Run(i) for i in range(len(self.layers))]
+        for i, r in enumerate(self.schedule):
+            if not 0 <= r.layer < len(self.layers):
+                raise ValueError(f"run {i} names layer {r.layer}, the model has {len(self.layers)}")
+            if r.reads_entry_of is not None:
+                if not 0 <= r.reads_entry_of < i or self.schedule[r.reads_entry_of].reads_entry_of is not None:
+                    raise ValueError(f"run {i} must read the cache of an earlier run that owns one")
+        if not self.vocab_size:
+            self.vocab_size = self.head.vocab
+
+
+class DecoderModel(Part):
+    def __init__(self, spec: DecoderSpec, opts: BuildOptions, config=None):
+        self.spec, self.opts, self.config = spec, opts, config
+        # cache entry of each run: its own index, or the index of the run it reads
+        self.entry_of_run = [r.reads_entry_of if r.reads_entry_of is not None else i
+                             for i, r in enumerate(spec.schedule)]
+
+    def children(self):
+        s = self.spec
+        out = [s.embedding, *s.layers, s.final_norm, s.head]
+        if s.position is not None:
+            out.append(s.position)
+        return out
+
+    def cache_entry_specs(self):
+        """For each run, the cache it owns (None for runs that read another run's)."""
+        out = []
+        for r in self.spec.schedule:
+            mixer = getattr(self.spec.layers[r.layer], "mixer", None)
+            own = r.reads_entry_of is None and mixer is not None
+            out.append(mixer.cache_spec() if own else None)
+        return out
+
+    def load_weights(self, source, where: str = "") -> int:
+        specs = self.param_specs()
+        check_names(specs, source.table(), where)
+        fetch = Fetcher(source, self.opts.device, self.opts.dtype)
+        self.load(fetch)
+        return fetch.bytes_loaded
+
+    def n_params(self) -> int:
+        seen, n = set(), 0
+        for s in self.param_specs():
+            if s.absent or s.name in seen:
+                continue
+            seen.add(s.name)
+            k = 1
+            for d in s.shape:
+                k *= d
+            n += k
+        return n
+
+    def forward(self, ctx, cache) -> torch.Tensor:
+        """Runs the step described by `ctx`; returns float32 logits [n_want, vocab]."""
+        s = self.spec
+        stream = HiddenStream(s.embedding.forward(ctx.tokens, ctx.n_tokens))
+        if s.position is not None:
+            s.position.add_to_embeddings(stream.residual, ctx)
+        for i, run in enumerate(s.schedule):
+            view = cache.entry_view(self.entry_of_run[i], ctx.block_tables)
+            s.layers[run.layer].forward(stream, ctx, view, write_cache=run.reads_entry_of is None)
+        if ctx.n_want == 0:
+            return torch.empty((0, s.vocab_size), dtype=torch.float32, device=stream.residual.device)
+        h = s.final_norm.forward(stream.residual, stream.delta, rows=ctx.want_rows, n_rows=ctx.n_want)
+        return s.head.forward(h, n_rows=ctx.n_want)[:ctx.n_want]

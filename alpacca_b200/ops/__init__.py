@@ -1,0 +1,225 @@
+"""Python side of the CUDA kernels: argument checks and the ctypes calls.
+
+Every function here runs a hand-written sm_100a kernel from `csrc/` on the
+current CUDA stream.  There is no CPU implementation behind them: tensors that
+are not on a CUDA device are refused, and a library that cannot be built or
+loaded raises.  Shapes, dtypes, strides and index ranges that a kernel relies
+on are checked here, on the host, before the launch, since a kernel given a
+bad pointer or size would fault the device rather than raise.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _lib(name):
+    return build.load(name)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _need(cond, msg):
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None:
+            _need(t.is_cuda, "alpacca_b200 kernels run on CUDA tensors only (there is no CPU path); "
+                  f"got a tensor on {t.device}")
+
+
+def _check(rc, what):
+    if rc != 0:
+        if rc >= 1000:
+            raise KernelError(f"{what}: CUDA error {rc - 1000} at launch")
+        raise KernelError(f"{what}: the kernel refused its arguments (code {rc})")
+
+
+def _dt(t):
+    _need(t.dtype in _DT, f"dtype {t.dtype} is not supported by the kernels (float32 or bfloat16)")
+    return _DT[t.dtype]
+
+
+def _i32(t, n=None, name="index tensor"):
+    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+    if n is not None:
+        _need(t.numel() >= n, f"{name} holds {t.numel()} entries, {n} needed")
+
+
+# ---------------------------------------------------------------------------
+
+def embed_rows(table, tokens, out):
+    """out[i,:] = table[tokens[i],:] as float32.  table [V,E] f32/bf16, tokens int32 [n], out f32 [n,E]."""
+    _cuda(table, tokens, out)
+    n = tokens.numel()
+    _i32(tokens, name="tokens")
+    _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be contiguous [V,E]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[-1] == table.shape[1]
+          and out.numel() >= n * table.shape[1], "embed_rows: out must be float32 [n,E]")
+    _check(_lib("elementwise").ab_embed_rows(_p(table), _dt(table), _p(tokens), _p(out), n,
+                                             table.shape[1], table.shape[0], _stream()), "embed_rows")
+    return out
+
+
+def add_rmsnorm(residual, delta, weight, eps, out, rows=None, n_rows=None):
+    """Fused residual add and RMSNorm.
+
+    residual f32 [T,E] (updated in place with `delta` when `rows` is None),
+    delta [T,E] of the activation dtype or None, weight f32 [E], out [n,E] of
+    the activation dtype or None (add only).  `rows` (int32 [n]) picks the
+    source rows and leaves the residual untouched.
+    """
+    _cuda(residual, delta, weight, out, rows)
+    E = residual.shape[-1]
+    T = residual.numel() // E
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "residual must be contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == E and weight.is_contiguous(),
+          "norm weight must be float32 [E]")
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.numel() == residual.numel(), "delta must match the residual")
+    if rows is not None:
+        n = rows.numel() if n_rows is None else n_rows
+        _i32(rows, n, "rows")
+    else:
+        n = T if n_rows is None else n_rows
+        _need(n <= T, "add_rmsnorm: more rows than the residual has")
+    act = out if out is not None else delta
+    _need(act is not None, "add_rmsnorm needs delta or out")
+    if out is not None:
+        _need(out.is_contiguous() and out.numel() >= n * E, "add_rmsnorm: out too small")
+        if delta is not None:
+            _need(out.dtype == delta.dtype, "add_rmsnorm: delta and out differ in dtype")
+    _check(_lib("elementwise").ab_add_rmsnorm(_p(residual), _p(delta), _p(weight), _p(out), _dt(act), _p(rows),
+                                              n, E, ctypes.c_float(eps), _stream()), "add_rmsnorm")
+    return out
+
+
+def add_bias(y, bias):
+    """y[t,j] += bias[j] in place; bias float32."""
+    _cuda(y, bias)
+    N = y.shape[-1]
+    _need(y.is_contiguous() and bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(),
+          "add_bias: y contiguous [..,N], bias float32 [N]")
+    _check(_lib("elementwise").ab_add_bias(_p(y), _dt(y), _p(bias), y.numel() // N, N, _stream()), "add_bias")
+    return y
+
+
+def rope_append(qkv, cos, sin, tok_pos, tok_seq, block_table, k_pages, v_pages, n_tokens, H, K, D,
+                n_rot, pairing, write_cache=True):
+    """Rotates q and k of `qkv` [T,(H+2K)D] by position and appends k, v to the pages.
+
+    cos/sin: float32 [P, n_rot/2] or None (no rotation); pairing 0 = (2i,2i+1),
+    1 = (i, n_rot/2+i).  k_pages/v_pages: [n_pages, K, page, D] of qkv's dtype.
+    The caller guarantees tok_pos < P and that the block table covers tok_pos.
+    """
+    _cuda(qkv, cos, sin, tok_pos, tok_seq, block_table, k_pages, v_pages)
+    _need(qkv.is_contiguous() and qkv.shape[-1] == (H + 2 * K) * D and qkv.numel() >= n_tokens * (H + 2 * K) * D,
+          "rope_append: qkv must be contiguous [T,(H+2K)*D]")
+    _i32(tok_pos, n_tokens, "tok_pos")
+    _i32(tok_seq, n_tokens, "tok_seq")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(),
+          "block_table must be contiguous int32 [B,W]")
+    if cos is not None:
+        _need(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32
+              and cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape
+              and cos.shape[-1] == n_rot // 2, "rope tables must be float32 [P, n_rot/2]")
+    page_size = k_pages.shape[2]
+    if write_cache:
+        _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype and k_pages.is_contiguous()
+              and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (K, page_size, D)
+              and k_pages.shape == v_pages.shape, "cache pages must be contiguous [n_pages,K,page,D] of qkv's dtype")
+    _check(_lib("elementwise").ab_rope_append(
+        _p(qkv), _dt(qkv), _p(cos), _p(sin), _p(tok_pos), _p(tok_seq), _p(block_table), block_table.shape[1],
+        _p(k_pages), _p(v_pages), n_tokens, H, K, D, n_rot, pairing, page_size, 1 if write_cache else 0,
+        _stream()), "rope_append")
+
+
+def swiglu(gu, out, n_rows=None):
+    """out[t,j] = silu(gate)*up from the fused, 8-row interleaved product gu [T,2F]."""
+    _cuda(gu, out)
+    F = gu.shape[-1] // 2
+    n = gu.numel() // (2 * F) if n_rows is None else n_rows
+    _need(gu.is_contiguous() and out.is_contiguous() and out.dtype == gu.dtype and out.shape[-1] == F
+          and out.numel() >= n * F and gu.numel() >= n * 2 * F, "swiglu: gu [T,2F], out [T,F], same dtype")
+    _need(F % 8 == 0, f"swiglu: the feed-forward width {F} must be a multiple of 8")
+    _check(_lib("elementwise").ab_swiglu(_p(gu), _p(out), _dt(gu), n, F, _stream()), "swiglu")
+    return out
+
+
+def attention_simt(qkv, out, k_pages, v_pages, block_table, tok_pos, tok_seq, n_tokens, H, K, D, scale,
+                   window=0):
+    """Attention of every token over its sequence's cached keys, 32-bit arithmetic.
+
+    qkv [T,(H+2K)D] (the q part is read), out [T,H*D].
+    """
+    _cuda(qkv, out, k_pages, v_pages, block_table, tok_pos, tok_seq)
+    _need(qkv.is_contiguous() and out.is_contiguous() and out.dtype == qkv.dtype and k_pages.dtype == qkv.dtype,
+          "attention: q, out and cache must share one dtype and be contiguous")
+    _need(out.numel() >= n_tokens * H * D, "attention: out too small")
+    _need(0 < D <= 256, f"attention (32-bit kernel): head size {D} is outside 1..256")
+    _i32(tok_pos, n_tokens, "tok_pos")
+    _i32(tok_seq, n_tokens, "tok_seq")
+    page_size = k_pages.shape[2]
+    _need(tuple(k_pages.shape[1:]) == (K, page_size, D) and k_pages.shape == v_pages.shape
+          and k_pages.is_contiguous() and v_pages.is_contiguous(), "attention: cache pages [n_pages,K,page,D]")
+    _check(_lib("attention_simt").ab_attention_simt(
+        _p(qkv), qkv.shape[-1], _p(out), _dt(qkv), _p(k_pages), _p(v_pages), _p(block_table),
+        block_table.shape[1], _p(tok_pos), _p(tok_seq), n_tokens, H, K, D, page_size, ctypes.c_float(scale),
+        int(window or 0), _stream()), "attention_simt")
+    return out
+
+
+def gemm_f32(a, w, out, bias=None, n_rows=None):
+    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) in true float32 (CUDA-core FMA, fixed k order)."""
+    _cuda(a, w, out, bias)
+    _need(a.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32,
+          "gemm_f32 takes float32 tensors")
+    K = a.shape[-1]
+    M = a.numel() // K if n_rows is None else n_rows
+    N = w.shape[0]
+    _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous() and w.dim() == 2 and w.shape[1] == K
+          and out.shape[-1] == N and out.numel() >= M * N and a.numel() >= M * K,
+          "gemm_f32: a [M,K], w [N,K], out [M,N], contiguous")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemm_f32: bias f32 [N]")
+    _check(_lib("gemm_f32").ab_gemm_f32_nt(_p(a), K, _p(w), K, _p(bias), _p(out), N, M, N, K, _stream()),
+           "gemm_f32")
+    return out
+
+
+def attention(qkv, out, cache, ctx, H, K, D, scale, window=0):
+    """Attention of the step's tokens over the paged cache (`cache`: a KVLayerView)."""
+    return attention_simt(qkv, out, cache.k, cache.v, cache.block_table, ctx.tok_pos, ctx.tok_seq,
+                          ctx.n_tokens, H, K, D, scale, window)
+
+
+def linear_bf16(x, w, out, n_rows=None):
+    """out[:n] = x[:n] @ w^T for bfloat16 x [M,K], w [N,K]; out bfloat16 or float32 [M,N]."""
+    _cuda(x, w, out)
+    n = x.shape[0] if n_rows is None else n_rows
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear_bf16 takes bfloat16 inputs")
+    _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and out.shape[-1] == w.shape[0],
+          "linear_bf16: x [M,K], w [N,K], out [M,N]")
+    if out.dtype == torch.float32:
+        torch.mm(x[:n], w.t(), out_dtype=torch.float32, out=out[:n])
+    else:
+        torch.mm(x[:n], w.t(), out=out[:n])
+    return out

@@ -1,0 +1,74 @@
+"""The matrix product y = x @ W^T (+ b), W stored [out, in] as in the checkpoint.
+
+Several checkpoint matrices that read the same input can be held as one fused
+matrix (q|k|v, gate|up).  In the 32-bit path the product is the package's own
+FMA kernel; in the bfloat16 path it is the skinny-matrix kernel for the few rows
+of a decode step and the library matrix product otherwise (the reference uses
+BLAS for every product: alpacca/tensor.py:82-97).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import ParamSpec
+from .base import BuildOptions, Part
+
+
+class Linear(Part):
+    def __init__(self, opts: BuildOptions, in_features: int, sources, bias: bool = False,
+                 interleave8: bool = False, out_dtype: torch.dtype | None = None):
+        """`sources`: list of (checkpoint prefix, rows); tensors `<prefix>.weight`
+        [rows, in] (and `<prefix>.bias` [rows]) are stacked in that order.
+        `interleave8`: two sources of equal size are interleaved in groups of 8
+        rows (8 of the first, 8 of the second, ...), the layout `ops.swiglu` reads.
+        `out_dtype` float32 gives float32 results from bfloat16 inputs (logits)."""
+        self.opts = opts
+        self.in_features = int(in_features)
+        self.sources = [(p, int(r)) for p, r in sources]
+        self.out_features = sum(r for _, r in self.sources)
+        self.has_bias = bool(bias)
+        self.interleave8 = bool(interleave8)
+        self.out_dtype = out_dtype or opts.dtype
+        if interleave8:
+            if len(self.sources) != 2 or self.sources[0][1] != self.sources[1][1] or self.sources[0][1] % 8:
+                raise ValueError("interleave8 needs two sources of equal size, a multiple of 8 rows "
+                                 f"(got {[r for _, r in self.sources]})")
+        self.weight = None
+        self.bias = None
+
+    def own_param_specs(self):
+        specs = [ParamSpec(f"{p}.weight", (r, self.in_features), "matrix", "normal") for p, r in self.sources]
+        if self.has_bias:
+            specs += [ParamSpec(f"{p}.bias", (r,), "vector", "normal") for p, r in self.sources]
+        return specs
+
+    def _stack(self, tensors):
+        if len(tensors) == 1:
+            return tensors[0]
+        if self.interleave8:
+            a, b = tensors
+            tail = a.shape[1:]
+            return torch.cat([a.reshape(-1, 8, *tail), b.reshape(-1, 8, *tail)], dim=1).reshape(-1, *tail).contiguous()
+        return torch.cat(tensors, dim=0).contiguous()
+
+    def load_own(self, fetch):
+        self.weight = self._stack([fetch(ParamSpec(f"{p}.weight", (r, self.in_features), "matrix"))
+                                   for p, r in self.sources])
+        if self.has_bias:
+            self.bias = self._stack([fetch(ParamSpec(f"{p}.bias", (r,), "vector")) for p, r in self.sources])
+
+    def share_weight(self, tensor: torch.Tensor):
+        """Uses an existing tensor as the matrix (a tied head)."""
+        self.weight = tensor
+
+    def forward(self, x: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
+        n = x.shape[0] if n_rows is None else n_rows
+        out = torch.empty((x.shape[0], self.out_features), dtype=self.out_dtype, device=x.device)
+        if x.dtype == torch.float32:
+            ops.gemm_f32(x, self.weight, out, bias=self.bias, n_rows=n)
+            return out
+        ops.linear_bf16(x, self.weight, out, n_rows=n)
+        if self.bias is not None:
+            ops.add_bias(out, self.bias)
+        return out
