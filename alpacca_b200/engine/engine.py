@@ -40,6 +40,12 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def room_for(self, token_counts) -> bool:
+        """Whether new sequences of these lengths fit together into what is free now."""
+        pages = sum(-(-int(n) // 64) for n in token_counts)
+        return (len(token_counts) <= self.cache.slots.n_free
+                and all(pages <= g.pages.n_free for g in self.cache.kv_groups))
+
     # -- the step ------------------------------------------------------------
     def _check(self, entries) -> None:
         if not entries:

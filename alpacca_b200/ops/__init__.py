@@ -223,3 +223,36 @@ def linear_bf16(x, w, out, n_rows=None):
     else:
         torch.mm(x[:n], w.t(), out=out[:n])
     return out
+
+
+def repeat_penalty(logits, recent, penalty):
+    """In place: for each distinct token of a row's window (int32 [B,R], -1 = unused),
+    l > 0 -> l / penalty, else l * penalty."""
+    _cuda(logits, recent)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(),
+          "repeat_penalty: logits float32 [B,V]")
+    _need(recent.dtype == torch.int32 and recent.dim() == 2 and recent.is_contiguous()
+          and recent.shape[0] == logits.shape[0], "repeat_penalty: recent int32 [B,R]")
+    _check(_lib("sampling").ab_repeat_penalty(_p(logits), _p(recent), logits.shape[0], recent.shape[1],
+                                              logits.shape[1], ctypes.c_float(penalty), _stream()),
+           "repeat_penalty")
+    return logits
+
+
+def sample(logits, out, temperature, top_k, top_p, seed, streams, steps):
+    """One token per row of float32 logits [B,V] into out int32 [B].
+
+    temperature <= 0: first index of the maximum.  Else top_k (<= 0: all), top_p
+    (>= 1: all), and a draw with Philox(seed; stream, step) per row.
+    """
+    _cuda(logits, out, streams, steps)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(),
+          "sample: logits float32 [B,V]")
+    B, V = logits.shape
+    _i32(out, B, "out")
+    _i32(streams, B, "streams")
+    _i32(steps, B, "steps")
+    _check(_lib("sampling").ab_sample(_p(logits), B, V, _p(out), ctypes.c_float(temperature), int(top_k),
+                                      ctypes.c_float(top_p), ctypes.c_uint64(int(seed) & (2**64 - 1)),
+                                      _p(streams), _p(steps), _stream()), "sample")
+    return out

@@ -1,0 +1,177 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16:
+whole requests, the last 32 tokens one by one, unequal batches one after another
+with slots used again, long decoding, the first tokens of a sequence."""
+import numpy as np
+import pytest
+import torch
+
+import tiny
+from helpers import CONFIGS, check_logits, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ("float32", "bfloat16")
+NAMES = ("a", "b", "c")
+
+
+def make_engine(model_dir, dtype, max_tokens=64 * 24, max_slots=8, max_positions=None):
+    from alpacca_b200.engine import Engine
+    from alpacca_b200.engine.loading import load_model_dir
+    model = load_model_dir(model_dir, dtype=dtype, device="cuda", max_positions=max_positions)
+    return Engine(model, max_tokens=max_tokens, max_slots=max_slots)
+
+
+def lengths_for(name):
+    top = CONFIGS[name]["max_position_embeddings"]
+    return [n for n in (1, 9, 33, 70, 64, 65, 127) if n <= top]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_each_request_alone_and_whole(model_dirs, name, dtype):
+    from alpacca_b200.engine import StepEntry
+    d = model_dirs[(name, dtype)]
+    eng = make_engine(d, dtype)
+    for i, n in enumerate(lengths_for(name)):
+        toks = tiny.prompt_tokens(CONFIGS[name], n, 100 + i)
+        slot = eng.alloc_slot()
+        got = eng.step([StepEntry(slot, toks, list(range(n)))]).cpu().numpy()
+        check_logits(got, plain_logits(d, toks), dtype, f"{name} whole n={n}")
+        eng.free_slot(slot)
+        eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_tokens_one_by_one(model_dirs, name, dtype):
+    from alpacca_b200.engine import StepEntry
+    d = model_dirs[(name, dtype)]
+    eng = make_engine(d, dtype)
+    for i, n in enumerate((33, 100)):
+        toks = tiny.prompt_tokens(CONFIGS[name], n, 200 + i)
+        want = plain_logits(d, toks)
+        slot = eng.alloc_slot()
+        head = n - 32
+        got = eng.step([StepEntry(slot, toks[:head], [head - 1])]).cpu().numpy()
+        check_logits(got[0], want[head - 1], dtype, f"{name} prefix of {n}")
+        for p in range(head, n):
+            got = eng.step([StepEntry(slot, [toks[p]], [0])]).cpu().numpy()
+            check_logits(got[0], want[p], dtype, f"{name} n={n} token {p} fed alone")
+        eng.free_slot(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_one_after_another(model_dirs, name, dtype):
+    """Batches of unequal prompts; every request is fed some more tokens one by one and the
+    shorter ones end earlier; the next batch takes the slots and pages that came back."""
+    from alpacca_b200.engine import StepEntry
+    d = model_dirs[(name, dtype)]
+    cfg = CONFIGS[name]
+    # room for one batch only, so that the second and third batches must reuse pages
+    eng = make_engine(d, dtype, max_tokens=64 * 7, max_slots=4)
+    top = cfg["max_position_embeddings"]
+    batches = [[(5, 3), (70, 9), (17, 1), (33, 12)], [(1, 20), (64, 2), (40, 6)], [(63, 4), (2, 2), (90, 11), (9, 0)]]
+    seen_slots = set()
+    for bi, batch in enumerate(batches):
+        reqs = []
+        for ri, (n_prompt, n_more) in enumerate(batch):
+            total = min(n_prompt + n_more, top)
+            toks = tiny.prompt_tokens(cfg, total, 300 + 10 * bi + ri)
+            reqs.append({"toks": toks, "prompt": min(n_prompt, total), "slot": eng.alloc_slot(),
+                         "want": plain_logits(d, toks)})
+        if bi:
+            assert {r["slot"] for r in reqs} & seen_slots, "later batches must reuse slots"
+        seen_slots |= {r["slot"] for r in reqs}
+        got = eng.step([StepEntry(r["slot"], r["toks"][:r["prompt"]], [r["prompt"] - 1]) for r in reqs])
+        got = got.cpu().numpy()
+        for row, r in enumerate(reqs):
+            check_logits(got[row], r["want"][r["prompt"] - 1], dtype, f"{name} batch {bi} prompt of req {row}")
+            r["pos"] = r["prompt"]
+        live = [r for r in reqs if r["pos"] < len(r["toks"])]
+        for r in reqs:
+            if r not in live:
+                eng.free_slot(r["slot"])
+        while live:
+            got = eng.step([StepEntry(r["slot"], [r["toks"][r["pos"]]], [0]) for r in live]).cpu().numpy()
+            nxt = []
+            for row, r in enumerate(live):
+                check_logits(got[row], r["want"][r["pos"]], dtype,
+                             f"{name} batch {bi} decode pos {r['pos']} (batch of {len(live)})")
+                r["pos"] += 1
+                if r["pos"] < len(r["toks"]):
+                    nxt.append(r)
+                else:
+                    eng.free_slot(r["slot"])
+            live = nxt
+            eng.cache.check()
+        assert eng.cache.slots.n_held == 0 and eng.cache.kv_groups[0].pages.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_dirs, dtype):
+    """A short prompt and then hundreds of single-token steps across several pages."""
+    from alpacca_b200.engine import StepEntry
+    name = "c"
+    d = model_dirs[(name, dtype)]
+    eng = make_engine(d, dtype, max_tokens=64 * 6)
+    toks = tiny.prompt_tokens(CONFIGS[name], 330, 400)
+    want = plain_logits(d, toks)
+    slot = eng.alloc_slot()
+    eng.step([StepEntry(slot, toks[:3], [])])
+    for p in range(3, len(toks)):
+        got = eng.step([StepEntry(slot, [toks[p]], [0])])
+        if p % 7 == 0 or p in (63, 64, 65, 127, 128, 129, 255, 256, 257, len(toks) - 1):
+            check_logits(got.cpu().numpy()[0], want[p], dtype, f"long decode pos {p}")
+    eng.free_slot(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    """A sequence that starts with a single token and grows one token at a time from
+    position 0, in a batch with a longer one."""
+    from alpacca_b200.engine import StepEntry
+    d = model_dirs[(name, dtype)]
+    eng = make_engine(d, dtype)
+    a = tiny.prompt_tokens(CONFIGS[name], 6, 500)
+    b = tiny.prompt_tokens(CONFIGS[name], 40, 501)
+    wa, wb = plain_logits(d, a), plain_logits(d, b)
+    sa, sb = eng.alloc_slot(), eng.alloc_slot()
+    got = eng.step([StepEntry(sa, a[:1], [0]), StepEntry(sb, b[:35], [0, 34])]).cpu().numpy()
+    check_logits(got[0], wa[0], dtype, "first token alone")
+    check_logits(got[1], wb[0], dtype, "first token of the longer one")
+    check_logits(got[2], wb[34], dtype, "last prompt token of the longer one")
+    for p in range(1, 6):
+        got = eng.step([StepEntry(sa, [a[p]], [0]), StepEntry(sb, [b[34 + p]], [0])]).cpu().numpy()
+        check_logits(got[0], wa[p], dtype, f"short sequence pos {p}")
+        check_logits(got[1], wb[34 + p], dtype, f"long sequence pos {34 + p}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_and_batch_do_not_change_a_result(model_dirs, dtype):
+    """The same request alone, in a batch, and cut into uneven steps gives the same logits
+    (equal up to rounding; in 32-bit the kernels make them equal to the last bit)."""
+    from alpacca_b200.engine import StepEntry
+    name = "b"
+    d = model_dirs[(name, dtype)]
+    eng = make_engine(d, dtype)
+    toks = tiny.prompt_tokens(CONFIGS[name], 75, 600)
+    other = tiny.prompt_tokens(CONFIGS[name], 120, 601)
+    s = eng.alloc_slot()
+    alone = eng.step([StepEntry(s, toks, list(range(75)))]).cpu().numpy()
+    eng.free_slot(s)
+    s1, s2 = eng.alloc_slot(), eng.alloc_slot()
+    both = eng.step([StepEntry(s1, other, [119]), StepEntry(s2, toks, list(range(75)))]).cpu().numpy()[1:]
+    eng.free_slot(s1)
+    eng.free_slot(s2)
+    s = eng.alloc_slot()
+    cut = [eng.step([StepEntry(s, toks[a:b], list(range(b - a)))]).cpu().numpy()
+           for a, b in ((0, 10), (10, 11), (11, 64), (64, 75))]
+    cut = np.concatenate(cut)
+    if dtype == "float32":
+        assert np.array_equal(alone, both), "a batch neighbour changed 32-bit logits"
+        assert np.abs(alone - cut).max() <= 2e-6
+    else:
+        assert np.abs(alone - both).max() <= 2e-2 and np.abs(alone - cut).max() <= 4e-2
+    check_logits(cut, plain_logits(d, toks), dtype, "cut into steps")

@@ -1,0 +1,277 @@
+"""Each kernel alone against a plain float32/float64 reference of the same operation,
+at sizes other than the engine's: widths and vocabularies that are no power of two,
+head sizes in steps of 16, several heads-per-group ratios."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# relative to the magnitude of the outputs (order 1 here): float32 sums of a few hundred
+# terms; bfloat16 results rounded once to 8 bits of mantissa
+TOL = {"float32": 2e-5, "bfloat16": 1.6e-2}
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).cuda()
+
+
+def close(got, want, dtype, what=""):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = (got - want).abs().max().item()
+    mag = max(want.abs().max().item(), 1.0)
+    assert math.isfinite(err) and err <= TOL[dtype] * mag, f"{what}: max err {err:.3e} (magnitude {mag:.2f})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("V,E", [(300, 72), (1003, 200)])
+def test_embed_rows(dtype, V, E):
+    from alpacca_b200 import ops
+    table = rnd(V, E, dtype=DT[dtype])
+    toks = torch.tensor([0, V - 1, 5, 5, 17], dtype=torch.int32).cuda()
+    out = torch.empty(5, E, dtype=torch.float32, device="cuda")
+    ops.embed_rows(table, toks, out)
+    assert torch.equal(out, table[toks.long()].float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,E,eps", [(1, 72, 1e-5), (7, 200, 1e-6), (33, 2056, 3e-6)])
+def test_add_rmsnorm(dtype, T, E, eps):
+    from alpacca_b200 import ops
+    res = rnd(T, E, seed=1)
+    delta = rnd(T, E, dtype=DT[dtype], seed=2)
+    w = 1 + rnd(E, seed=3) * 0.1
+    want_res = res.double() + delta.double()
+    want = want_res / torch.sqrt((want_res ** 2).mean(-1, keepdim=True) + eps) * w.double()
+    r = res.clone()
+    out = torch.empty(T, E, dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(r, delta, w, eps, out)
+    close(out, want, dtype, "normed")
+    close(r, want_res, "float32", "residual after the add")
+    # rows: picked rows only, residual untouched
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32).cuda()
+    r2 = res.clone()
+    out2 = torch.empty(2, E, dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(r2, delta, w, eps, out2, rows=rows)
+    close(out2, want[[T - 1, 0]], dtype, "picked rows")
+    assert torch.equal(r2, res)
+    # without delta
+    out3 = torch.empty(T, E, dtype=DT[dtype], device="cuda")
+    ops.add_rmsnorm(res.clone(), None, w, eps, out3)
+    want3 = res.double() / torch.sqrt((res.double() ** 2).mean(-1, keepdim=True) + eps) * w.double()
+    close(out3, want3, dtype, "no delta")
+
+
+def ref_rope(x, pos, n_rot, pairing, cos, sin):
+    """x [T, heads, D] float64."""
+    x = x.clone()
+    half = n_rot // 2
+    c, s = cos[pos][:, None, :].double(), sin[pos][:, None, :].double()
+    if pairing == 0:
+        a, b = x[..., 0:n_rot:2].clone(), x[..., 1:n_rot:2].clone()
+        x[..., 0:n_rot:2], x[..., 1:n_rot:2] = a * c - b * s, a * s + b * c
+    else:
+        a, b = x[..., :half].clone(), x[..., half:n_rot].clone()
+        x[..., :half], x[..., half:n_rot] = a * c - b * s, a * s + b * c
+    return x
+
+
+def make_paged(lengths, n_pages, K, D, dtype, page=64, seed=0):
+    """Block table with pages handed out in a scattered order; returns table, k/v pages."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-n // page) for n in lengths)
+    table = torch.zeros(len(lengths), width, dtype=torch.int32)
+    for b, n in enumerate(lengths):
+        for i in range(-(-n // page)):
+            table[b, i] = perm.pop()
+    k = torch.zeros(n_pages, K, page, D, dtype=dtype, device="cuda")
+    v = torch.zeros_like(k)
+    return table.cuda(), k, v
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,K,D,n_rot,pairing", [(4, 4, 16, 16, 0), (6, 2, 32, 32, 1), (10, 5, 48, 32, 1),
+                                                 (3, 1, 80, 40, 0)])
+def test_rope_append(dtype, H, K, D, n_rot, pairing):
+    from alpacca_b200 import ops
+    lengths = [70, 3, 130]           # tokens already there + new ones; new tokens are the last q_len
+    q_lens = [5, 3, 66]
+    table, kp, vp = make_paged(lengths, 8, K, D, DT[dtype])
+    T = sum(q_lens)
+    qkv = rnd(T, (H + 2 * K) * D, dtype=DT[dtype], seed=5)
+    pos = torch.cat([torch.arange(n - q, n) for n, q in zip(lengths, q_lens)]).to(torch.int32)
+    seq = torch.cat([torch.full((q,), b) for b, q in enumerate(q_lens)]).to(torch.int32)
+    P = 160
+    inv = 10000.0 ** (-torch.arange(n_rot // 2, dtype=torch.float64) * 2 / n_rot)
+    ang = torch.arange(P, dtype=torch.float64)[:, None] * inv
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    x = qkv.double().cpu().view(T, H + 2 * K, D)
+    want_qk = ref_rope(x[:, :H + K], pos.long(), n_rot, pairing, cos.cpu(), sin.cpu())
+    got = qkv.clone()
+    ops.rope_append(got, cos, sin, pos.cuda(), seq.cuda(), table, kp, vp, T, H, K, D, n_rot, pairing)
+    g = got.double().cpu().view(T, H + 2 * K, D)
+    close(g[:, :H], want_qk[:, :H], dtype, "q rotated in place")
+    tb = table.cpu()
+    for t in range(T):
+        page, off = tb[seq[t], pos[t] // 64].item(), pos[t].item() % 64
+        close(kp[page, :, off], want_qk[t, H:], dtype, f"k of token {t} in the cache")
+        close(vp[page, :, off], x[t, H + K:], dtype, f"v of token {t} in the cache")
+    # padding tokens are skipped
+    got2, kp2 = qkv.clone(), torch.zeros_like(kp)
+    ops.rope_append(got2, cos, sin, pos.cuda(), torch.full_like(seq, -1).cuda(), table, kp2, torch.zeros_like(vp),
+                    T, H, K, D, n_rot, pairing)
+    assert torch.equal(got2, qkv) and kp2.abs().sum().item() == 0
+
+
+def ref_attention(q, k, v, pos_q, scale, window=0):
+    """q [Tq,H,D], k/v [S,K,D] float64, pos_q: position of each query."""
+    Tq, H, D = q.shape
+    G = H // k.shape[1]
+    out = torch.zeros(Tq, H, D, dtype=torch.float64)
+    for t in range(Tq):
+        p = int(pos_q[t])
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(H):
+            sc = (k[lo:p + 1, h // G] @ q[t, h]) * scale
+            out[t, h] = torch.softmax(sc, 0) @ v[lo:p + 1, h // G]
+    return out
+
+
+def fill_cache(table, kp, vp, b, kk, vv):
+    for s in range(kk.shape[0]):
+        page = table[b, s // 64].item()
+        kp[page, :, s % 64] = kk[s].to(kp.dtype)
+        vp[page, :, s % 64] = vv[s].to(vp.dtype)
+
+
+ATT_CASES = [(4, 4, 16), (6, 2, 32), (10, 5, 48), (8, 1, 64), (5, 5, 80), (4, 2, 128), (2, 1, 256), (14, 2, 96)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,K,D", ATT_CASES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_prefill_and_decode(dtype, H, K, D, window):
+    """Three sequences in one launch: a prompt from position 0, a chunk on top of cached
+    tokens, and a single decode token far into its sequence."""
+    from alpacca_b200 import ops
+    from alpacca_b200.cache import KVLayerView
+    from types import SimpleNamespace
+    lengths, q_lens = [75, 200, 301], [75, 40, 1]
+    table, kp, vp = make_paged(lengths, 12, K, D, DT[dtype], seed=D)
+    T = sum(q_lens)
+    qkv = rnd(T, (H + 2 * K) * D, dtype=DT[dtype], seed=7)
+    ks = [rnd(n, K, D, dtype=DT[dtype], seed=8 + b) for b, n in enumerate(lengths)]
+    vs = [rnd(n, K, D, dtype=DT[dtype], seed=11 + b) for b, n in enumerate(lengths)]
+    for b in range(3):
+        fill_cache(table.cpu(), kp, vp, b, ks[b], vs[b])
+    pos = torch.cat([torch.arange(n - q, n) for n, q in zip(lengths, q_lens)]).to(torch.int32)
+    seq = torch.cat([torch.full((q,), b) for b, q in enumerate(q_lens)]).to(torch.int32)
+    scale = D ** -0.5
+    out = torch.empty(T, H * D, dtype=DT[dtype], device="cuda")
+    cu = torch.tensor([0, 75, 115, 116], dtype=torch.int32).cuda()
+    ctx = SimpleNamespace(tok_pos=pos.cuda(), tok_seq=seq.cuda(), n_tokens=T, n_seqs=3, cu_q=cu,
+                          kv_len=torch.tensor(lengths, dtype=torch.int32).cuda(), is_decode=False,
+                          host_q_lens=q_lens, host_kv_lens=lengths, max_q_len=75, max_kv_len=301, extras={})
+    ops.attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, scale, window)
+    q = qkv.double().cpu().view(T, H + 2 * K, D)[:, :H]
+    t0 = 0
+    for b, (n, ql) in enumerate(zip(lengths, q_lens)):
+        want = ref_attention(q[t0:t0 + ql], ks[b].double().cpu(), vs[b].double().cpu(), pos[t0:t0 + ql], scale, window)
+        close(out[t0:t0 + ql].view(ql, H, D), want, dtype, f"sequence {b}")
+        t0 += ql
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key(dtype):
+    """Among hundreds of keys one, far back and on another page, matches the query: the
+    output must be its value.  A kernel that skips, misplaces or masks that key shows here."""
+    from alpacca_b200 import ops
+    from alpacca_b200.cache import KVLayerView
+    from types import SimpleNamespace
+    H, K, D, n = 4, 2, 64, 700
+    table, kp, vp = make_paged([n], 16, K, D, DT[dtype], seed=3)
+    kk = rnd(n, K, D, seed=1) * 0.1
+    vv = rnd(n, K, D, seed=2)
+    qkv = torch.zeros(1, (H + 2 * K) * D, device="cuda")
+    far = {0: 5, 1: 64, 2: 383, 3: 699}      # page starts, page ends, the first and the very last key
+    for h, s in far.items():
+        direction = torch.zeros(D, device="cuda")
+        direction[h * 7] = 1.0
+        kk[s, h // 2] = direction * 30.0
+        qkv[0, h * D:(h + 1) * D] = direction * 30.0
+    fill_cache(table.cpu(), kp, vp, 0, kk, vv)
+    qkv = qkv.to(DT[dtype])
+    out = torch.empty(1, H * D, dtype=DT[dtype], device="cuda")
+    ctx = SimpleNamespace(tok_pos=torch.tensor([n - 1], dtype=torch.int32).cuda(),
+                          tok_seq=torch.zeros(1, dtype=torch.int32).cuda(), n_tokens=1, n_seqs=1,
+                          cu_q=torch.tensor([0, 1], dtype=torch.int32).cuda(),
+                          kv_len=torch.tensor([n], dtype=torch.int32).cuda(), is_decode=True,
+                          host_q_lens=[1], host_kv_lens=[n], max_q_len=1, max_kv_len=n, extras={})
+    ops.attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, 0)
+    for h, s in far.items():
+        want = vp[table[0, s // 64].item(), h // 2, s % 64].float()
+        got = out[0, h * D:(h + 1) * D].float()
+        assert (got - want).abs().max().item() < 2e-2, f"head {h} did not find key {s}"
+    # with a window the far keys are cut off, except the last one, which lies inside it
+    ops.attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, 100)
+    want = vp[table[0, 699 // 64].item(), 1, 699 % 64].float()
+    assert (out[0, 3 * D:].float() - want).abs().max().item() < 2e-2
+    # the window's edge: position n-100 is the first key inside, n-101 the last one outside
+    kk2 = kk.clone()
+    kk2[600, 0] = kk[5, 0]       # head 0's matching key, now on the edge
+    kk2[599, 1] = kk[383, 1]     # head 2's matching key, now just outside (its old place 383 is outside too)
+    fill_cache(table.cpu(), kp, vp, 0, kk2, vv)
+    ops.attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, 100)
+    edge = vp[table[0, 600 // 64].item(), 0, 600 % 64].float()
+    assert (out[0, :D].float() - edge).abs().max().item() < 2e-2, "the key on the window's edge was not seen"
+    outside = vp[table[0, 599 // 64].item(), 1, 599 % 64].float()
+    assert (out[0, 2 * D:3 * D].float() - outside).abs().max().item() > 0.1, "a key outside the window was seen"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,F", [(1, 160), (9, 264), (70, 1000)])
+def test_swiglu(dtype, T, F):
+    from alpacca_b200 import ops
+    gate, up = rnd(T, F, seed=1) * 3, rnd(T, F, seed=2)
+    gu = torch.cat([gate.view(T, F // 8, 8), up.view(T, F // 8, 8)], dim=2).reshape(T, 2 * F).to(DT[dtype])
+    g, u = gu.view(T, F // 8, 2, 8)[:, :, 0].reshape(T, F).double(), gu.view(T, F // 8, 2, 8)[:, :, 1].reshape(T, F).double()
+    out = torch.empty(T, F, dtype=DT[dtype], device="cuda")
+    ops.swiglu(gu, out)
+    close(out, g / (1 + torch.exp(-g)) * u, dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 72, 200), (5, 1003, 120), (70, 264, 333), (130, 64, 64)])
+def test_gemm_f32(M, N, K):
+    from alpacca_b200 import ops
+    a, w, bias = rnd(M, K, seed=1), rnd(N, K, seed=2), rnd(N, seed=3)
+    out = torch.empty(M, N, device="cuda")
+    ops.gemm_f32(a, w, out, bias=bias)
+    close(out, a.double() @ w.double().T + bias.double(), "float32")
+    # a row's result does not depend on the rows beside it
+    out1 = torch.empty(1, N, device="cuda")
+    ops.gemm_f32(a[M // 2:M // 2 + 1].contiguous(), w, out1, bias=bias)
+    assert torch.equal(out1[0], out[M // 2])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 72, 200), (3, 1003, 120), (8, 264, 328), (16, 520, 64), (70, 264, 336)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_linear_bf16(M, N, K, out_dtype):
+    from alpacca_b200 import ops
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    out = torch.empty(M, N, dtype=DT[out_dtype], device="cuda")
+    ops.linear_bf16(a, w, out)
+    want = a.double() @ w.double().T
+    close(out, want, out_dtype if out_dtype == "bfloat16" else "float32", "linear_bf16")
+
+
+def test_add_bias():
+    from alpacca_b200 import ops
+    y, b = rnd(7, 72, dtype=torch.bfloat16), rnd(72, seed=4)
+    want = y.float() + b
+    ops.add_bias(y, b)
+    close(y, want, "bfloat16")
