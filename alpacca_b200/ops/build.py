@@ -44,7 +44,13 @@ def _find_nvcc() -> str:
                      "the CUDA kernels of alpacca_b200 cannot be built")
 
 
+_chosen_dir: Path | None = None
+
+
 def _build_dir() -> Path:
+    global _chosen_dir
+    if _chosen_dir is not None:
+        return _chosen_dir
     override = os.environ.get("ALPACCA_B200_BUILD_DIR")
     cands = [Path(override)] if override else []
     cands.append(CSRC / "_build")
@@ -52,9 +58,9 @@ def _build_dir() -> Path:
     for d in cands:
         try:
             d.mkdir(parents=True, exist_ok=True)
-            probe = d / f".w{os.getpid()}"
-            probe.write_bytes(b"")
-            probe.unlink()
+            with tempfile.NamedTemporaryFile(dir=d, prefix=".probe"):
+                pass
+            _chosen_dir = d
             return d
         except OSError:
             continue
@@ -107,7 +113,7 @@ def library_path(name: str) -> Path:
     stamp = out_dir / f"lib{name}.stamp"
     if lib.is_file() and stamp.is_file() and stamp.read_text().strip() == fp:
         return lib
-    tmp = out_dir / f"lib{name}.{os.getpid()}.tmp.so"
+    tmp = out_dir / f"lib{name}.{os.getpid()}.{threading.get_ident()}.tmp.so"
     if is_cuda:
         cmd = [_find_nvcc(), *flags, "-I", str(CSRC), "-o", str(tmp), str(src)]
     else:

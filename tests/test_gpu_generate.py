@@ -1,0 +1,120 @@
+"""Generation through the Python entry point and the command line, against the plain loop."""
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import plain_llama as plain
+import tiny
+from helpers import CONFIGS, plain_model
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def margin_ok(model_dir, prompt, tokens, tol):
+    """Every generated token is the plain model's argmax for the same prefix, or within `tol` of it."""
+    pm = plain_model(str(model_dir))
+    seq = list(prompt)
+    for t in tokens:
+        row = pm.logits(seq)[-1]
+        if row[t] < row.max() - tol:
+            return False
+        seq.append(t)
+    return True
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_greedy_generation_of_an_unequal_batch(model_dirs, name, dtype):
+    from alpacca_b200.api import Model, generate
+    from alpacca_b200.sampling import SamplerParams
+    d = model_dirs[(name, dtype)]
+    cfg = CONFIGS[name]
+    lens = (5, 11, 17) if name == "a" else (1, 9, 33, 70)
+    prompts = [tiny.prompt_tokens(cfg, n, 700 + i) for i, n in enumerate(lens)]
+    model = Model.load(d, dtype=dtype, max_batch=4)
+    res = generate(model, prompts, SamplerParams.greedy(), n_predict=8, stop_token_ids=[])
+    stops = set(model.decoder.spec.stop_token_ids)
+    for p, r in zip(prompts, res):
+        want, _ = plain.generate(plain_model(str(d)), p, 8, stop=stops)
+        if dtype == "float32":
+            kept = [t for t in want if t not in stops]
+            assert r.token_ids == kept and r.tokens == len(want)
+        assert margin_ok(d, p, r.token_ids, 1e-4 if dtype == "float32" else 0.08)
+        assert r.finish_reason in ("length", "stop") and r.prompt_tokens == len(p)
+    one = generate(model, prompts[1], SamplerParams.greedy(), n_predict=8)
+    assert one.token_ids == res[1].token_ids, "a request alone and in a batch must give the same tokens"
+    # more requests than a batch holds: batches one after another
+    many = generate(model, prompts * 3, SamplerParams.greedy(), n_predict=4)
+    assert [r.token_ids for r in many[:len(prompts)]] == [r.token_ids[:4] for r in res]
+    assert [r.token_ids for r in many[len(prompts):2 * len(prompts)]] == [r.token_ids[:4] for r in res]
+    assert model.engine.cache.slots.n_held == 0
+
+
+def test_stop_token_and_context_end_sequences(model_dirs):
+    from alpacca_b200.api import Model, generate
+    from alpacca_b200.sampling import SamplerParams
+    d = model_dirs[("a", "float32")]
+    p = tiny.prompt_tokens(tiny.TINY_A, 6, 710)
+    model = Model.load(d, dtype="float32", n_ctx=16)
+    free = generate(model, p, SamplerParams.greedy(), n_predict=6)
+    assert free.tokens == 6
+    stopped = generate(model, p, SamplerParams.greedy(), n_predict=6, stop_token_ids=[free.token_ids[2]])
+    assert stopped.token_ids == free.token_ids[:2] and stopped.tokens == 3 and stopped.finish_reason == "stop"
+    full = generate(model, p, SamplerParams.greedy(), n_predict=-1)       # until the 16 positions are used
+    assert len(p) + full.tokens <= 16 and full.finish_reason in ("context", "length", "stop")
+
+
+def test_temperature_sampling_is_seeded_and_batch_independent(model_dirs):
+    from alpacca_b200.api import Model, generate
+    from alpacca_b200.sampling import SamplerParams
+    d = model_dirs[("b", "float32")]
+    prompts = [tiny.prompt_tokens(tiny.TINY_B, n, 720 + i) for i, n in enumerate((1, 9, 33, 70))]
+    model = Model.load(d, dtype="float32", max_batch=4)
+    params = SamplerParams(temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=11)
+    a = generate(model, prompts, params, n_predict=12, stop_token_ids=[])
+    b = generate(model, prompts, params, n_predict=12, stop_token_ids=[])
+    assert [r.token_ids for r in a] == [r.token_ids for r in b]
+    c = generate(model, prompts, SamplerParams(temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=12),
+                 n_predict=12)
+    assert [r.token_ids for r in a] != [r.token_ids for r in c]
+    # the plain loop with the same seed and stream gives the same tokens
+    stops = set(model.decoder.spec.stop_token_ids)
+    for i in (0, 2):
+        want, _ = plain.generate(plain_model(str(d)), prompts[i], 12, temperature=0.8, seed=11, stream=i, stop=stops)
+        assert a[i].token_ids == [t for t in want if t not in stops]
+
+
+def test_reference_style_single_sequence_calls(model_dirs):
+    from alpacca_b200.api import Model
+    d = model_dirs[("c", "float32")]
+    toks = tiny.prompt_tokens(tiny.TINY_C, 20, 730)
+    want = plain_model(str(d)).logits(toks)
+    model = Model.load(d, dtype="float32")
+    got = model.prefill(toks[:15]).cpu().numpy()
+    assert np.abs(got - want[14]).max() < 5e-5 and model.n_past == 15
+    for p in range(15, 20):
+        got = model.forward(toks[p]).cpu().numpy()
+        assert np.abs(got - want[p]).max() < 5e-5
+    model.reset()
+    assert model.n_past == 0
+    assert "LlamaForCausalLM" in model.describe()
+
+
+def test_command_line(model_dirs):
+    d = model_dirs[("a", "float32")]
+    p = tiny.prompt_tokens(tiny.TINY_A, 5, 740)
+    cmd = [sys.executable, "-m", "alpacca_b200", "run", str(d), " ".join(map(str, p)), "/", "7 8 9",
+           "-n", "6", "--temp", "0", "--repeat-penalty", "1.0", "--dtype", "float32", "--seed", "1"]
+    out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    lines = out.stdout.strip().splitlines()
+    assert len(lines) == 2 and "tokens," in out.stderr
+    want, _ = plain.generate(plain_model(str(d)), p, 6, stop={2})
+    assert [int(t) for t in lines[0].split()] == [t for t in want if t != 2]
+    bad = subprocess.run([sys.executable, "-m", "alpacca_b200", "run", str(d), "hello"], cwd=ROOT,
+                         capture_output=True, text=True, timeout=600)
+    assert bad.returncode == 1 and "alpacca_b200: error:" in bad.stderr
