@@ -1,0 +1,495 @@
+// Causal grouped-query attention over the paged cache on the tensor cores,
+// bfloat16 operands, float32 scores, softmax and accumulators.
+//
+// Two kernels share the inner tile code (flash attention: running maximum and
+// sum per row, keys visited page by page; a page of the cache, 64 keys of one
+// KV head, is exactly one key tile):
+//
+//   prefill  one CTA per (tile of query rows, KV head).  A row is a pair
+//            (token, head of the group): the G query heads that share a KV head
+//            sit in the same tile, so a key tile is loaded once for all of
+//            them.  Any mix of sequences: tokens on top of cached ones, chunks,
+//            single tokens; the host lists the tiles.
+//   decode   one new token per sequence: one CTA per (sequence, KV head, chunk
+//            of keys); each warp takes one page of the chunk, the warps'
+//            results are merged in shared memory, the chunks' in a second
+//            kernel, always in chunk order (the result does not depend on
+//            which CTA finishes first).
+//
+// Scores: (q.k) * scale; key s is seen by a token at position p iff
+// lo <= s <= p, lo = max(0, p - window + 1) (window 0: all)
+// (alpacca/model.py:447-467).  Head sizes: multiples of 16 up to 256.
+#include "common.cuh"
+#include <cuda_pipeline.h>
+
+#define PAGE 64
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                                  uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+               "{%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// Running state of one warp's 16 rows; thread (g = lane/4, t = lane%4) holds rows g and g+8.
+template <int DMAX>
+struct RowState {
+  float o[DMAX / 8][4];
+  float m[2];   // running maximum of score * scale * log2(e)
+  float l[2];   // running sum of 2^(score' - m)
+};
+
+// One key tile (64 keys) for one warp.
+//   qs: this warp's 16 query rows in shared memory, pitch `pitch` elements
+//   ks, vs: the key and value tile [64][pitch]
+//   pos0/pos1, lo0/lo1: last and first visible key of rows g and g+8; key0: position of the tile's first key
+template <int DMAX>
+__device__ __forceinline__ void attend_tile(RowState<DMAX>& st, const bf16* qs, const bf16* ks, const bf16* vs,
+                                            int pitch, int D, float scale_log2, int key0, int pos0, int pos1,
+                                            int lo0, int lo1, bool need_mask) {
+  const int lane = threadIdx.x & 31;
+  const int t = lane & 3;
+  float s[8][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+
+  // S = Q K^T
+  const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+  const int b_key = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+#pragma unroll
+  for (int kd = 0; kd < DMAX / 16; ++kd) {
+    if (kd * 16 < D) {
+      uint32_t a0, a1, a2, a3;
+      ldmatrix_x4(a0, a1, a2, a3, smem_u32(qs + a_row * pitch + kd * 16 + a_col));
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, smem_u32(ks + (np * 16 + b_key) * pitch + kd * 16 + b_col));
+        mma_bf16(s[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+
+  // scale, mask, running softmax
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v = s[nt][j] * scale_log2;
+      if (need_mask) {
+        const int key = key0 + nt * 8 + 2 * t + (j & 1);
+        const bool ok = (j < 2) ? (key <= pos0 && key >= lo0) : (key <= pos1 && key >= lo1);
+        if (!ok) v = -INFINITY;
+      }
+      s[nt][j] = v;
+      if (j < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+    }
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+  // a row that has seen no key yet keeps m = -inf; subtract 0 then, so that exp2(-inf - 0) = 0
+  const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
+  const float corr0 = exp2f(st.m[0] - sub0), corr1 = exp2f(st.m[1] - sub1);
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    s[nt][0] = exp2f(s[nt][0] - sub0);
+    s[nt][1] = exp2f(s[nt][1] - sub0);
+    s[nt][2] = exp2f(s[nt][2] - sub1);
+    s[nt][3] = exp2f(s[nt][3] - sub1);
+    sum0 += s[nt][0] + s[nt][1];
+    sum1 += s[nt][2] + s[nt][3];
+  }
+  st.m[0] = mn0;
+  st.m[1] = mn1;
+  st.l[0] = st.l[0] * corr0 + sum0;   // per-thread partial sums; the quad is reduced at the end
+  st.l[1] = st.l[1] * corr1 + sum1;
+#pragma unroll
+  for (int dt = 0; dt < DMAX / 8; ++dt) {
+    st.o[dt][0] *= corr0;
+    st.o[dt][1] *= corr0;
+    st.o[dt][2] *= corr1;
+    st.o[dt][3] *= corr1;
+  }
+
+  // O += P V
+  const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
+#pragma unroll
+  for (int ks16 = 0; ks16 < 4; ++ks16) {
+    const uint32_t a0 = pack_bf16(s[2 * ks16][0], s[2 * ks16][1]);
+    const uint32_t a1 = pack_bf16(s[2 * ks16][2], s[2 * ks16][3]);
+    const uint32_t a2 = pack_bf16(s[2 * ks16 + 1][0], s[2 * ks16 + 1][1]);
+    const uint32_t a3 = pack_bf16(s[2 * ks16 + 1][2], s[2 * ks16 + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < DMAX / 16; ++dp) {
+      if (dp * 16 < D) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vs + (ks16 * 16 + v_key) * pitch + dp * 16 + v_col));
+        mma_bf16(st.o[2 * dp], a0, a1, a2, a3, b0, b1);
+        mma_bf16(st.o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+}
+
+template <int DMAX>
+__device__ __forceinline__ void init_state(RowState<DMAX>& st) {
+#pragma unroll
+  for (int dt = 0; dt < DMAX / 8; ++dt) st.o[dt][0] = st.o[dt][1] = st.o[dt][2] = st.o[dt][3] = 0.f;
+  st.m[0] = st.m[1] = -INFINITY;
+  st.l[0] = st.l[1] = 0.f;
+}
+
+// copies one page tile [64][D] (contiguous in global memory) into shared memory [64][pitch]
+__device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int D, int pitch, int tid, int nthreads) {
+  const int cpr = D >> 3;                 // 16-byte chunks per row
+  for (int c = tid; c < PAGE * cpr; c += nthreads) {
+    const int r = c / cpr, cc = c - r * cpr;
+    cp_async_16(dst + r * pitch + cc * 8, src + (size_t)r * D + cc * 8);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// prefill
+// ---------------------------------------------------------------------------
+template <int DMAX>
+__global__ void __launch_bounds__(128)
+attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
+                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_pos,
+                         const int* __restrict__ cu_q, const int* __restrict__ tile_seq,
+                         const int* __restrict__ tile_q0, int H, int K, int D, float scale_log2, int window,
+                         int tokens_per_tile) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int pitch = D + 8;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);            // [64][pitch]
+  bf16* kbuf = qs + 64 * pitch;                            // [2][64][pitch]
+  bf16* vbuf = kbuf + 2 * 64 * pitch;                      // [2][64][pitch]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int G = H / K;
+  const int b = tile_seq[blockIdx.x];
+  const int q0 = tile_q0[blockIdx.x];
+  const int kh = blockIdx.y;
+  const int q_end = cu_q[b + 1];
+  const int n_tok = min(tokens_per_tile, q_end - q0);
+  const int n_rows = n_tok * G;
+
+  // stage Q rows: row r = (token q0 + r / G, head kh*G + r % G); rows past the end are zero
+  {
+    const int cpr = D >> 3;
+    for (int c = tid; c < 64 * cpr; c += 128) {
+      const int r = c / cpr, cc = c - r * cpr;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < n_rows) {
+        const int tok = q0 + r / G, h = kh * G + r % G;
+        v = *reinterpret_cast<const uint4*>(qkv + (size_t)tok * q_stride + (size_t)h * D + cc * 8);
+      }
+      *reinterpret_cast<uint4*>(qs + r * pitch + cc * 8) = v;
+    }
+  }
+  // positions of this thread's two rows
+  const int r0 = warp * 16 + g, r1 = r0 + 8;
+  const int BIG = 0x3fffffff;
+  int pos0 = BIG, pos1 = BIG, lo0 = 0, lo1 = 0;
+  if (r0 < n_rows) { pos0 = tok_pos[q0 + r0 / G]; lo0 = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0; }
+  if (r1 < n_rows) { pos1 = tok_pos[q0 + r1 / G]; lo1 = (window > 0 && pos1 - window + 1 > 0) ? pos1 - window + 1 : 0; }
+  const int pos_first = tok_pos[q0], pos_last = tok_pos[q0 + n_tok - 1];
+  const int kb_begin = (window > 0 && pos_first - window + 1 > 0) ? (pos_first - window + 1) / PAGE : 0;
+  const int kb_end = pos_last / PAGE + 1;
+  const int* bt = block_table + (size_t)b * table_width;
+
+  RowState<DMAX> st;
+  init_state(st);
+
+  auto issue = [&](int kb, int stage) {
+    const size_t base = ((size_t)bt[kb] * K + kh) * PAGE * D;
+    load_tile_async(kbuf + stage * 64 * pitch, k_pages + base, D, pitch, tid, 128);
+    load_tile_async(vbuf + stage * 64 * pitch, v_pages + base, D, pitch, tid, 128);
+    cp_async_commit();
+  };
+  issue(kb_begin, 0);
+  for (int kb = kb_begin; kb < kb_end; ++kb) {
+    const int stage = (kb - kb_begin) & 1;
+    if (kb + 1 < kb_end) { issue(kb + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const int key0 = kb * PAGE;
+    // rows of this warp that exist at all; a warp without rows still joins the barriers
+    if (warp * 16 < n_rows) {
+      const bool need_mask = (key0 + PAGE - 1 > pos_first) || (window > 0);
+      attend_tile<DMAX>(st, qs + warp * 16 * pitch, kbuf + stage * 64 * pitch, vbuf + stage * 64 * pitch, pitch, D,
+                        scale_log2, key0, pos0, pos1, lo0, lo1, need_mask);
+    }
+    __syncthreads();
+  }
+
+  // finish: reduce the row sums over the quad, normalise, store
+  float l0 = st.l[0], l1 = st.l[1];
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+#pragma unroll
+  for (int dt = 0; dt < DMAX / 8; ++dt) {
+    if (dt * 8 < D) {
+      const int d = dt * 8 + 2 * t4;
+      if (r0 < n_rows) {
+        bf16* o = out + ((size_t)(q0 + r0 / G) * H + kh * G + r0 % G) * D + d;
+        *reinterpret_cast<uint32_t*>(o) = pack_bf16(st.o[dt][0] * inv0, st.o[dt][1] * inv0);
+      }
+      if (r1 < n_rows) {
+        bf16* o = out + ((size_t)(q0 + r1 / G) * H + kh * G + r1 % G) * D + d;
+        *reinterpret_cast<uint32_t*>(o) = pack_bf16(st.o[dt][2] * inv1, st.o[dt][3] * inv1);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// decode: one token per sequence; grid (sequence, KV head x row tile, chunk)
+// ---------------------------------------------------------------------------
+template <int DMAX, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
+                        float* __restrict__ part_o, float* __restrict__ part_ml,
+                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                        const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
+                        const int* __restrict__ kv_len, int H, int K, int D, float scale_log2, int window,
+                        int n_chunks) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int pitch = D + 8;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][pitch]
+  bf16* kv = qs + 16 * pitch;                                   // [NWARPS][2][64][pitch]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int G = H / K;
+  const int row_tiles = (G + 15) / 16;
+  const int tok = blockIdx.x;
+  const int kh = blockIdx.y / row_tiles, rt = blockIdx.y - kh * row_tiles;
+  const int chunk = blockIdx.z;
+  const int b = tok_seq[tok];
+  if (b < 0) return;
+  const int len = kv_len[b];
+  const int pos = len - 1;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int keys_per_chunk = NWARPS * PAGE;
+  const int first_chunk = lo / keys_per_chunk, last_chunk = pos / keys_per_chunk;
+  if (chunk < first_chunk || chunk > last_chunk) return;
+  const int n_rows = min(16, G - rt * 16);
+
+  {
+    const int cpr = D >> 3;
+    for (int c = tid; c < 16 * cpr; c += NWARPS * 32) {
+      const int r = c / cpr, cc = c - r * cpr;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < n_rows)
+        v = *reinterpret_cast<const uint4*>(qkv + (size_t)tok * q_stride + (size_t)(kh * G + rt * 16 + r) * D + cc * 8);
+      *reinterpret_cast<uint4*>(qs + r * pitch + cc * 8) = v;
+    }
+  }
+  RowState<DMAX> st;
+  init_state(st);
+  const int page_idx = chunk * NWARPS + warp;
+  const int key0 = page_idx * PAGE;
+  const bool active = key0 <= pos && key0 + PAGE - 1 >= lo;
+  bf16* ks = kv + (size_t)warp * 2 * 64 * pitch;
+  bf16* vs = ks + 64 * pitch;
+  if (active) {
+    const size_t base = ((size_t)block_table[(size_t)b * table_width + page_idx] * K + kh) * PAGE * D;
+    load_tile_async(ks, k_pages + base, D, pitch, lane, 32);
+    load_tile_async(vs, v_pages + base, D, pitch, lane, 32);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  if (active) {
+    const bool need_mask = (key0 + PAGE - 1 > pos) || (key0 < lo);
+    attend_tile<DMAX>(st, qs, ks, vs, pitch, D, scale_log2, key0, pos, pos, lo, lo, need_mask);
+  }
+  float l0 = st.l[0], l1 = st.l[1];
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();      // every warp is done with its tiles: shared memory is reused below
+
+  // merge the warps: sm_o [NWARPS][16][D], sm_m, sm_l [NWARPS][16]
+  float* sm_o = reinterpret_cast<float*>(kv);
+  float* sm_m = sm_o + NWARPS * 16 * D;
+  float* sm_l = sm_m + NWARPS * 16;
+#pragma unroll
+  for (int dt = 0; dt < DMAX / 8; ++dt) {
+    if (dt * 8 < D) {
+      const int d = dt * 8 + 2 * t4;
+      sm_o[(warp * 16 + g) * D + d] = st.o[dt][0];
+      sm_o[(warp * 16 + g) * D + d + 1] = st.o[dt][1];
+      sm_o[(warp * 16 + g + 8) * D + d] = st.o[dt][2];
+      sm_o[(warp * 16 + g + 8) * D + d + 1] = st.o[dt][3];
+    }
+  }
+  if (t4 == 0) {
+    sm_m[warp * 16 + g] = st.m[0];
+    sm_m[warp * 16 + g + 8] = st.m[1];
+    sm_l[warp * 16 + g] = l0;
+    sm_l[warp * 16 + g + 8] = l1;
+  }
+  __syncthreads();
+  const bool single = (first_chunk == last_chunk);
+  for (int idx = tid; idx < n_rows * D; idx += NWARPS * 32) {
+    const int r = idx / D, d = idx - r * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) m = fmaxf(m, sm_m[w * 16 + r]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+      const float mw = sm_m[w * 16 + r];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      l += sm_l[w * 16 + r] * f;
+      o += sm_o[(w * 16 + r) * D + d] * f;
+    }
+    const int h = kh * G + rt * 16 + r;
+    if (single) {
+      out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    } else {
+      const size_t p = ((size_t)tok * H + h) * n_chunks + chunk;
+      part_o[p * D + d] = o;
+      if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
+    }
+  }
+}
+
+// merges the chunks of one (token, head) in chunk order
+__global__ void attention_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                              const float* __restrict__ part_ml, const int* __restrict__ tok_seq,
+                                              const int* __restrict__ kv_len, int H, int D, int window,
+                                              int keys_per_chunk, int n_chunks) {
+  const int tok = blockIdx.x, h = blockIdx.y;
+  const int b = tok_seq[tok];
+  if (b < 0) return;
+  const int pos = kv_len[b] - 1;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int first = lo / keys_per_chunk, last = pos / keys_per_chunk;
+  if (first == last) return;            // the decode kernel wrote the result itself
+  const size_t base = ((size_t)tok * H + h) * n_chunks;
+  float m = -INFINITY;
+  for (int c = first; c <= last; ++c) m = fmaxf(m, part_ml[(base + c) * 2]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float l = 0.f, o = 0.f;
+    for (int c = first; c <= last; ++c) {
+      const float mc = part_ml[(base + c) * 2];
+      const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - m);
+      l += part_ml[(base + c) * 2 + 1] * f;
+      o += part_o[(base + c) * D + d] * f;
+    }
+    out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// entry points
+// ---------------------------------------------------------------------------
+static int dmax_of(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : 256); }
+
+// keys that one decode CTA covers, for head size D (the caller sizes the scratch with it)
+AB_API int ab_attention_decode_chunk(int D) { return (dmax_of(D) == 256 ? 2 : 4) * PAGE; }
+
+AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
+                                     const void* v_pages, const int* block_table, int table_width,
+                                     const int* tok_pos, const int* cu_q, const int* tile_seq, const int* tile_q0,
+                                     int n_tiles, int tokens_per_tile, int H, int K, int D, float scale, int window,
+                                     cudaStream_t stream) {
+  if (n_tiles <= 0) return AB_OK;
+  if (D <= 0 || D > 256 || (D % 16) || H % K || K > 65535) return AB_BAD_ARG;
+  const int G = H / K;
+  if (tokens_per_tile < 1 || tokens_per_tile * G > 64) return AB_BAD_ARG;
+  const int pitch = D + 8;
+  const size_t smem = (size_t)(64 + 4 * 64) * pitch * sizeof(bf16);
+  dim3 grid(n_tiles, K);
+  const float sl = scale * LOG2E;
+#define AB_GO(DM)                                                                                                  \
+  {                                                                                                                \
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DM>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                               \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
+    attention_prefill_kernel<DM><<<grid, 128, smem, stream>>>(                                                     \
+        (const bf16*)qkv, q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages, block_table,           \
+        table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, D, sl, window, tokens_per_tile);                      \
+  }
+  switch (dmax_of(D)) {
+    case 64: AB_GO(64); break;
+    case 128: AB_GO(128); break;
+    default: AB_GO(256); break;
+  }
+#undef AB_GO
+  return ab_launch_status();
+}
+
+AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
+                                    const void* k_pages, const void* v_pages, const int* block_table,
+                                    int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
+                                    int K, int D, float scale, int window, int n_chunks, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535) return AB_BAD_ARG;
+  const int G = H / K, row_tiles = (G + 15) / 16;
+  if ((long long)K * row_tiles > 65535) return AB_BAD_ARG;
+  const int pitch = D + 8;
+  const float sl = scale * LOG2E;
+  dim3 grid(n_tokens, K * row_tiles, n_chunks);
+#define AB_GO(DM, NW)                                                                                               \
+  {                                                                                                                 \
+    size_t tiles = (size_t)(16 + NW * 2 * 64) * pitch * sizeof(bf16);                                               \
+    size_t merge = (size_t)16 * pitch * sizeof(bf16) + (size_t)NW * 16 * (D + 2) * sizeof(float);                   \
+    size_t smem = tiles > merge ? tiles : merge;                                                                    \
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DM, NW>,                                           \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
+    attention_decode_kernel<DM, NW><<<grid, NW * 32, smem, stream>>>(                                               \
+        (const bf16*)qkv, q_stride, (bf16*)out, part_o, part_ml, (const bf16*)k_pages, (const bf16*)v_pages,        \
+        block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, n_chunks);                                  \
+  }
+  int keys_per_chunk;
+  switch (dmax_of(D)) {
+    case 64: AB_GO(64, 4); keys_per_chunk = 4 * PAGE; break;
+    case 128: AB_GO(128, 4); keys_per_chunk = 4 * PAGE; break;
+    default: AB_GO(256, 2); keys_per_chunk = 2 * PAGE; break;
+  }
+#undef AB_GO
+  int rc = ab_launch_status();
+  if (rc != AB_OK || n_chunks == 1) return rc;
+  attention_decode_merge_kernel<<<dim3(n_tokens, H), 64, 0, stream>>>((bf16*)out, part_o, part_ml, tok_seq, kv_len,
+                                                                      H, D, window, keys_per_chunk, n_chunks);
+  return ab_launch_status();
+}

@@ -46,7 +46,12 @@ def _cuda(*tensors):
                   f"got a tensor on {t.device}")
 
 
+launches = 0     # kernels of this package launched so far (the benchmark reports the count)
+
+
 def _check(rc, what):
+    global launches
+    launches += 1
     if rc != 0:
         if rc >= 1000:
             raise KernelError(f"{what}: CUDA error {rc - 1000} at launch")
@@ -205,26 +210,125 @@ def gemm_f32(a, w, out, bias=None, n_rows=None):
     return out
 
 
+GEMV_MAX_ROWS = 16          # more rows go to the library matrix product
+
+
+def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False):
+    """out[:n] = x[:n] @ w^T (+ bias) for n <= 32 rows, bfloat16 x [M,K], w [N,K].
+
+    out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row interleaved gate|up
+    matrix [2F,K] and out is bfloat16 [M,F] = silu(gate) * up.
+    """
+    _cuda(x, w, out, bias)
+    n = x.shape[0] if n_rows is None else n_rows
+    K = x.shape[1]
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+          and w.dim() == 2 and w.shape[1] == K and out.is_contiguous(), "gemv_bf16: x [M,K], w [N,K] bfloat16")
+    _need(0 < n <= 32 and n <= x.shape[0] and n <= out.shape[0], f"gemv_bf16 takes 1..32 rows, got {n}")
+    _need(K % 8 == 0, f"gemv_bf16: the inner size {K} must be a multiple of 8")
+    if swiglu:
+        _need(N % 16 == 0 and out.dtype == torch.bfloat16 and out.shape[-1] == N // 2,
+              "gemv_bf16 swiglu: w [2F,K] with F a multiple of 8, out bfloat16 [M,F]")
+        epi = 2
+    else:
+        _need(out.shape[-1] == N and out.dtype in (torch.bfloat16, torch.float32), "gemv_bf16: out [M,N]")
+        epi = 1 if out.dtype == torch.float32 else 0
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemv_bf16: bias f32 [N]")
+    _check(_lib("gemv_bf16").ab_gemv_bf16(_p(x), _p(w), _p(bias), _p(out), n, N, K, out.shape[-1], epi, _stream()),
+           "gemv_bf16")
+    return out
+
+
+def _prefill_tiles(ctx, G, device):
+    """Tiles of query tokens for the tensor-core prefill kernel: (sequence, first packed token),
+    longest key ranges first.  Planned once per step and group size."""
+    key = ("attention_tiles", G)
+    plan = ctx.extras.get(key)
+    if plan is None:
+        tpt = max(1, 64 // G)
+        tiles, start = [], 0
+        for b, (q, kv) in enumerate(zip(ctx.host_q_lens, ctx.host_kv_lens)):
+            for q0 in range(0, q, tpt):
+                tiles.append((kv - q + min(q0 + tpt, q), b, start + q0))
+            start += q
+        tiles.sort(key=lambda x: -x[0])
+        t = torch.tensor([[x[1] for x in tiles], [x[2] for x in tiles]], dtype=torch.int32).to(device)
+        plan = (t[0].contiguous(), t[1].contiguous(), len(tiles), tpt)
+        ctx.extras[key] = plan
+    return plan
+
+
+def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
+    """Tensor-core attention (bfloat16) over the paged cache; prefill or decode by the step's kind."""
+    k_pages, v_pages, table = cache.k, cache.v, cache.block_table
+    _cuda(qkv, out, k_pages, v_pages, table)
+    T = ctx.n_tokens
+    _need(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
+          and qkv.is_contiguous() and out.is_contiguous(), "attention_mma takes contiguous bfloat16 tensors")
+    _need(D % 16 == 0 and 0 < D <= 256 and H % K == 0 and H // K <= 64,
+          f"attention_mma: head size {D} (multiples of 16 up to 256) or group size {H // K} (up to 64) not supported")
+    _need(qkv.shape[-1] == (H + 2 * K) * D and out.numel() >= T * H * D, "attention_mma: qkv [T,(H+2K)D], out [T,H*D]")
+    page = k_pages.shape[2]
+    _need(page == 64 and tuple(k_pages.shape[1:]) == (K, 64, D) and k_pages.shape == v_pages.shape
+          and k_pages.is_contiguous() and v_pages.is_contiguous(), "attention_mma: cache pages [n_pages,K,64,D]")
+    lib = _lib("attention_mma")
+    if ctx.is_decode:
+        chunk = lib.ab_attention_decode_chunk(D)
+        n_chunks = max(1, -(-min(ctx.max_kv_len, table.shape[1] * 64) // chunk))
+        if n_chunks > 1:
+            part_o = torch.empty((T * H * n_chunks, D), dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty((T * H * n_chunks, 2), dtype=torch.float32, device=qkv.device)
+        else:
+            part_o = part_ml = None
+        _i32(ctx.tok_seq, T, "tok_seq")
+        _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
+        _check(lib.ab_attention_decode_bf16(
+            _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(k_pages), _p(v_pages), _p(table),
+            table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0),
+            n_chunks, _stream()), "attention_decode")
+        return out
+    tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // K, qkv.device)
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+    _check(lib.ab_attention_prefill_bf16(
+        _p(qkv), qkv.shape[-1], _p(out), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
+        _p(ctx.cu_q), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, K, D, ctypes.c_float(scale), int(window or 0),
+        _stream()), "attention_prefill")
+    return out
+
+
 def attention(qkv, out, cache, ctx, H, K, D, scale, window=0):
-    """Attention of the step's tokens over the paged cache (`cache`: a KVLayerView)."""
+    """Attention of the step's tokens over the paged cache (`cache`: a KVLayerView).
+
+    bfloat16 with a head size in steps of 16 up to 256: the tensor-core kernels; everything
+    else (the 32-bit path, other head sizes up to 256): the 32-bit kernel."""
+    if qkv.dtype == torch.bfloat16 and D % 16 == 0 and D <= 256 and H // K <= 64:
+        return attention_mma(qkv, out, cache, ctx, H, K, D, scale, window)
     return attention_simt(qkv, out, cache.k, cache.v, cache.block_table, ctx.tok_pos, ctx.tok_seq,
                           ctx.n_tokens, H, K, D, scale, window)
 
 
-def linear_bf16(x, w, out, n_rows=None):
-    """out[:n] = x[:n] @ w^T for bfloat16 x [M,K], w [N,K]; out bfloat16 or float32 [M,N]."""
+def linear_bf16(x, w, out, n_rows=None, bias=None):
+    """out[:n] = x[:n] @ w^T (+ bias) for bfloat16 x [M,K], w [N,K]; out bfloat16 or float32 [M,N].
+
+    Up to GEMV_MAX_ROWS rows (decode steps): the skinny-matrix kernel, which reads the weights
+    once.  More rows: the library matrix product (as the reference uses BLAS)."""
     _cuda(x, w, out)
     n = x.shape[0] if n_rows is None else n_rows
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear_bf16 takes bfloat16 inputs")
     _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and out.shape[-1] == w.shape[0],
           "linear_bf16: x [M,K], w [N,K], out [M,N]")
+    if n <= GEMV_MAX_ROWS and x.shape[1] % 8 == 0:
+        return gemv_bf16(x, w, out, bias=bias, n_rows=n)
     if out.dtype == torch.float32:
         torch.mm(x[:n], w.t(), out_dtype=torch.float32, out=out[:n])
     else:
         torch.mm(x[:n], w.t(), out=out[:n])
+    if bias is not None:
+        add_bias(out[:n], bias)
     return out
-
-
 def repeat_penalty(logits, recent, penalty):
     """In place: for each distinct token of a row's window (int32 [B,R], -1 = unused),
     l > 0 -> l / penalty, else l * penalty."""

@@ -6,9 +6,6 @@ one product feeds the activation kernel.
 """
 from __future__ import annotations
 
-import torch
-
-from .. import ops
 from .base import BuildOptions, FeedForward
 from .linear import Linear
 
@@ -27,7 +24,5 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx):
         T = ctx.n_tokens
-        gu = self.gate_up.forward(h, n_rows=T)
-        act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
-        ops.swiglu(gu, act, n_rows=T)
+        act = self.gate_up.forward_swiglu(h, n_rows=T)
         return self.down.forward(act, n_rows=T)

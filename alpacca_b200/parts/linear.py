@@ -68,7 +68,12 @@ class Linear(Part):
         if x.dtype == torch.float32:
             ops.gemm_f32(x, self.weight, out, bias=self.bias, n_rows=n)
             return out
-        ops.linear_bf16(x, self.weight, out, n_rows=n)
-        if self.bias is not None:
-            ops.add_bias(out, self.bias)
-        return out
+        return ops.linear_bf16(x, self.weight, out, n_rows=n, bias=self.bias)
+
+    def forward_swiglu(self, x: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
+        """silu(gate) * up of the interleaved gate|up product, [M, out_features / 2]."""
+        n = x.shape[0] if n_rows is None else n_rows
+        act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
+        if x.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.in_features % 8 == 0:
+            return ops.gemv_bf16(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True)
+        return ops.swiglu(self.forward(x, n_rows=n), act, n_rows=n)

@@ -275,3 +275,96 @@ def test_add_bias():
     want = y.float() + b
     ops.add_bias(y, b)
     close(y, want, "bfloat16")
+
+
+def decode_ctx(lengths):
+    from types import SimpleNamespace
+    B = len(lengths)
+    return SimpleNamespace(
+        tok_pos=torch.tensor([n - 1 for n in lengths], dtype=torch.int32).cuda(),
+        tok_seq=torch.arange(B, dtype=torch.int32).cuda(), n_tokens=B, n_seqs=B,
+        cu_q=torch.arange(B + 1, dtype=torch.int32).cuda(), kv_len=torch.tensor(lengths, dtype=torch.int32).cuda(),
+        is_decode=True, host_q_lens=[1] * B, host_kv_lens=list(lengths), max_q_len=1, max_kv_len=max(lengths),
+        extras={})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,K,D", ATT_CASES + [(40, 2, 64)])
+@pytest.mark.parametrize("window", [0, 130])
+def test_attention_decode_batch(dtype, H, K, D, window):
+    """One token per sequence, lengths from 1 to beyond a thousand keys (one to several chunks)."""
+    from alpacca_b200 import ops
+    from alpacca_b200.cache import KVLayerView
+    lengths = [1, 64, 65, 300, 700, 1025]
+    table, kp, vp = make_paged(lengths, 40, K, D, DT[dtype], seed=D + H)
+    B = len(lengths)
+    qkv = rnd(B, (H + 2 * K) * D, dtype=DT[dtype], seed=17)
+    ks = [rnd(n, K, D, dtype=DT[dtype], seed=18 + b) for b, n in enumerate(lengths)]
+    vs = [rnd(n, K, D, dtype=DT[dtype], seed=31 + b) for b, n in enumerate(lengths)]
+    for b in range(B):
+        fill_cache(table.cpu(), kp, vp, b, ks[b], vs[b])
+    ctx = decode_ctx(lengths)
+    out = torch.empty(B, H * D, dtype=DT[dtype], device="cuda")
+    ops.attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, window)
+    q = qkv.double().cpu().view(B, H + 2 * K, D)[:, :H]
+    for b, n in enumerate(lengths):
+        want = ref_attention(q[b:b + 1], ks[b].double().cpu(), vs[b].double().cpu(), [n - 1], D ** -0.5, window)
+        close(out[b].view(1, H, D), want, dtype, f"sequence of {n}")
+    # a padded row (tok_seq -1) is skipped and leaves its output alone
+    ctx.tok_seq[2] = -1
+    out2 = torch.full_like(out, 7.0)
+    ops.attention(qkv, out2, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, window)
+    assert torch.equal(out2[2], torch.full_like(out2[2], 7.0)) and torch.equal(out2[3], out[3])
+
+
+@pytest.mark.parametrize("H,K,D", [(6, 2, 32), (8, 1, 64), (3, 3, 72)])
+def test_attention_32bit_kernel_on_bfloat16(H, K, D):
+    """The 32-bit kernel also serves bfloat16 tensors (head sizes the tensor-core kernel refuses)."""
+    from alpacca_b200 import ops
+    lengths = [5, 200]
+    table, kp, vp = make_paged(lengths, 6, K, D, torch.bfloat16, seed=D)
+    qkv = rnd(2, (H + 2 * K) * D, dtype=torch.bfloat16, seed=3)
+    ks = [rnd(n, K, D, dtype=torch.bfloat16, seed=4 + b) for b, n in enumerate(lengths)]
+    vs = [rnd(n, K, D, dtype=torch.bfloat16, seed=6 + b) for b, n in enumerate(lengths)]
+    for b in range(2):
+        fill_cache(table.cpu(), kp, vp, b, ks[b], vs[b])
+    ctx = decode_ctx(lengths)
+    out = torch.empty(2, H * D, dtype=torch.bfloat16, device="cuda")
+    ops.attention_simt(qkv, out, kp, vp, table, ctx.tok_pos, ctx.tok_seq, 2, H, K, D, D ** -0.5, 0)
+    q = qkv.double().cpu().view(2, H + 2 * K, D)[:, :H]
+    for b, n in enumerate(lengths):
+        want = ref_attention(q[b:b + 1], ks[b].double().cpu(), vs[b].double().cpu(), [n - 1], D ** -0.5)
+        close(out[b].view(1, H, D), want, "bfloat16")
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 27, 32])
+@pytest.mark.parametrize("N,K", [(72, 200), (1003, 120), (2048, 2048), (264, 8200)])
+def test_gemv_bf16(M, N, K):
+    from alpacca_b200 import ops
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.1), rnd(N, seed=3)
+    want = x.double() @ w.double().T + bias.double()
+    for dt, tol in ((torch.float32, "float32"), (torch.bfloat16, "bfloat16")):
+        out = torch.full((M, N), 9.0, dtype=dt, device="cuda")
+        ops.gemv_bf16(x, w, out, bias=bias)
+        close(out, want, tol, f"gemv {dt}")
+    # fewer rows than the buffers hold: the rest is left alone
+    if M > 1:
+        out = torch.full((M, N), 9.0, dtype=torch.float32, device="cuda")
+        ops.gemv_bf16(x, w, out, n_rows=M - 1)
+        assert (out[M - 1] == 9.0).all()
+        close(out[:M - 1], (x.double() @ w.double().T)[:M - 1], "float32")
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 160, 64), (7, 264, 120), (16, 1000, 328)])
+def test_gemv_bf16_swiglu_epilogue(M, F, K):
+    from alpacca_b200 import ops
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    gate, up = rnd(F, K, dtype=torch.bfloat16, seed=2, scale=0.3), rnd(F, K, dtype=torch.bfloat16, seed=3, scale=0.3)
+    bg, bu = rnd(F, seed=4), rnd(F, seed=5)
+    w = torch.cat([gate.view(F // 8, 8, K), up.view(F // 8, 8, K)], dim=1).reshape(2 * F, K).contiguous()
+    bias = torch.cat([bg.view(F // 8, 8), bu.view(F // 8, 8)], dim=1).reshape(2 * F).contiguous()
+    g = x.double() @ gate.double().T + bg.double()
+    u = x.double() @ up.double().T + bu.double()
+    out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    ops.gemv_bf16(x, w, out, bias=bias, swiglu=True)
+    close(out, g / (1 + torch.exp(-g)) * u, "bfloat16", "swiglu epilogue")
