@@ -37,6 +37,9 @@ class Model:
         self.engine = Engine(decoder, max_tokens=tokens, max_slots=max(self.max_batch, 1),
                              max_positions=self.n_ctx)
         self.load_seconds = 0.0
+        # decode steps are replayed from CUDA graphs when every part of the model allows it
+        self.use_graphs = self.engine.device.type == "cuda" and decoder.all_capturable()
+        self._decoders: dict = {}
         self._slot = None            # the single sequence of prefill()/forward()/reset()
         self.cached_ids: list[int] = []
 
@@ -112,6 +115,21 @@ class Model:
         self.cached_ids.append(int(token))
         return logits[0]
 
+    def decoder_for(self, sampler):
+        """The decoder of single-token steps for this sampler's options (graphs are captured per
+        batch shape and per set of options, and kept)."""
+        from .engine.decode import EagerDecoder, GraphDecoder
+        if not self.use_graphs:
+            return EagerDecoder(self.engine, sampler)
+        p = sampler.params
+        key = (p.temperature, p.top_k, p.top_p, p.repeat_penalty if p.penalizes else 1.0,
+               p.repeat_last_n if p.penalizes else 0)
+        dec = self._decoders.get(key)
+        if dec is None:
+            dec = self._decoders[key] = GraphDecoder(self.engine, sampler)
+        dec.reset(sampler)
+        return dec
+
     def describe(self) -> str:
         c, d = self.config, self.decoder
         dt = {torch.bfloat16: "bfloat16", torch.float32: "float32"}[d.opts.dtype]
@@ -134,7 +152,8 @@ def generate(model: Model, prompt_ids, params: SamplerParams | None = None, n_pr
     stop = set(model.decoder.spec.stop_token_ids) | set(stop_token_ids or ())
     sampler = DeviceSampler(params, model.engine.device)
     results = generate_requests(model.engine, sampler, prompts, n_predict, stop, model.max_batch,
-                                bos_token_id=getattr(model.config, "bos_token_id", None), on_token=stream)
+                                bos_token_id=getattr(model.config, "bos_token_id", None), on_token=stream,
+                                decoder=model.decoder_for(sampler))
     return results[0] if single else results
 
 

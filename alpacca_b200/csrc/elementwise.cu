@@ -239,3 +239,44 @@ AB_API int ab_swiglu(const void* gu, void* act, int dtype, int n_rows, int F, cu
     return AB_BAD_ARG;
   return ab_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// After a decode step whose tokens were sampled on the device: feed them back.
+// For every live row b (tok_seq[b] >= 0): tokens[b] = sampled[b]; position,
+// length and the sampler's step counter go up by one; the token enters the
+// row's window of recent tokens (a ring of `window` places, next place in
+// recent_pos[b]).  The sampled tokens of all rows are also kept in
+// history[(*counter % history_len)][:] for the host to read later.
+// ---------------------------------------------------------------------------
+__global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ tok_pos, int* __restrict__ kv_len,
+                                      int* __restrict__ rng_step, const int* __restrict__ tok_seq,
+                                      const int* __restrict__ sampled, int* __restrict__ recent,
+                                      int* __restrict__ recent_pos, int window, int* __restrict__ history,
+                                      int* __restrict__ counter, int history_len, int n_rows) {
+  const int slot = history ? (*counter % history_len) : 0;
+  for (int b = threadIdx.x; b < n_rows; b += blockDim.x) {
+    const int tok = sampled[b];
+    if (history) history[(size_t)slot * n_rows + b] = tok;
+    if (tok_seq[b] < 0) continue;
+    tokens[b] = tok;
+    tok_pos[b] += 1;
+    kv_len[b] += 1;
+    rng_step[b] += 1;
+    if (recent && window > 0) {
+      const int p = recent_pos[b];
+      recent[(size_t)b * window + p] = tok;
+      recent_pos[b] = (p + 1) % window;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && counter) *counter += 1;
+}
+
+AB_API int ab_decode_advance(int* tokens, int* tok_pos, int* kv_len, int* rng_step, const int* tok_seq,
+                             const int* sampled, int* recent, int* recent_pos, int window, int* history,
+                             int* counter, int history_len, int n_rows, cudaStream_t stream) {
+  if (n_rows <= 0) return AB_OK;
+  decode_advance_kernel<<<1, 256, 0, stream>>>(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent,
+                                               recent_pos, window, history, counter, history_len, n_rows);
+  return ab_launch_status();
+}

@@ -135,8 +135,8 @@ __device__ void block_scan(unsigned long long w, unsigned int c, unsigned long l
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out, float temperature, int top_k,
-              float top_p, unsigned int seed_lo, unsigned int seed_hi, const int* __restrict__ streams,
-              const int* __restrict__ steps) {
+              float top_p, unsigned int seed_lo, unsigned int seed_hi, const unsigned int* __restrict__ seed_dev,
+              const int* __restrict__ streams, const int* __restrict__ steps) {
   __shared__ SampleShared sh;
   const int row = blockIdx.x;
   const float* l = logits + (size_t)row * vocab;
@@ -327,6 +327,10 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   unsigned int ce, ct;
   block_scan(my_w, 0u, &w_before, &ce, &w_total, &ct, &sh);
 
+  if (seed_dev) {            // the seed lives on the device when the launch is replayed from a graph
+    seed_lo = seed_dev[0];
+    seed_hi = seed_dev[1];
+  }
   unsigned int x0;
   philox4x32_10((unsigned int)steps[row], 0u, (unsigned int)streams[row], 0u, seed_lo, seed_hi, &x0);
   const double u = (double)(x0 >> 8) * (1.0 / 16777216.0);
@@ -354,12 +358,12 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
 }
 
 AB_API int ab_sample(const float* logits, int n_rows, int vocab, int* out, float temperature, int top_k,
-                     float top_p, unsigned long long seed, const int* streams, const int* steps,
-                     cudaStream_t stream) {
+                     float top_p, unsigned long long seed, const unsigned int* seed_dev, const int* streams,
+                     const int* steps, cudaStream_t stream) {
   if (n_rows <= 0) return AB_OK;
   if (vocab <= 0) return AB_BAD_ARG;
   sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, out, temperature, top_k, top_p,
                                                        (unsigned int)(seed & 0xffffffffull),
-                                                       (unsigned int)(seed >> 32), streams, steps);
+                                                       (unsigned int)(seed >> 32), seed_dev, streams, steps);
   return ab_launch_status();
 }

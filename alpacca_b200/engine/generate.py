@@ -67,11 +67,17 @@ def plan_batches(prompt_lens, n_predict: int, max_positions: int, max_batch: int
 
 
 def generate_requests(engine, sampler, prompts, n_predict: int = -1, stop_token_ids=(), max_batch: int = 8,
-                      bos_token_id=None, on_token=None, timer=time.perf_counter) -> list[GenerationResult]:
+                      bos_token_id=None, on_token=None, timer=time.perf_counter,
+                      decoder=None) -> list[GenerationResult]:
     """Generates for every prompt (a list of token ids); returns results in the order of the prompts.
 
-    `on_token(request index, token)` is called for every token that is kept.
+    `on_token(request index, token)` is called for every token that is kept.  `decoder` runs the
+    single-token steps (`step(live) -> tokens`, see engine/decode.py); by default every step is one
+    `engine.step` and one `sampler.sample`.
     """
+    if decoder is None:
+        from .decode import EagerDecoder
+        decoder = EagerDecoder(engine, sampler)
     prompts = [list(p) for p in prompts]
     for i, p in enumerate(prompts):
         if not p:
@@ -95,24 +101,20 @@ def generate_requests(engine, sampler, prompts, n_predict: int = -1, stop_token_
                 results[i].seconds = timer() - t0
                 engine.free_slot(slots.pop(i))
 
-            # rows of `logits` follow `live`; sequences that cannot sample drop out first
-            rows = list(range(len(live)))
+            # a sequence whose prompt already fills the context cannot sample at all
+            rows = []
+            for r, i in enumerate(live):
+                if engine.length(slots[i]) >= max_pos:
+                    finish(i, "context")
+                elif budgets[i] <= 0:
+                    finish(i, "length")
+                else:
+                    rows.append(r)
+            if len(rows) != len(live):
+                live = [live[r] for r in rows]
+                logits = logits[rows].contiguous() if rows else None
+            tokens = sampler.sample(logits, [states[i] for i in live]) if live else []
             while live:
-                keep_rows, keep_live = [], []
-                for r, i in zip(rows, live):
-                    if engine.length(slots[i]) >= max_pos:
-                        finish(i, "context")
-                    elif budgets[i] <= 0:
-                        finish(i, "length")
-                    else:
-                        keep_rows.append(r)
-                        keep_live.append(i)
-                live = keep_live
-                if not live:
-                    break
-                if keep_rows != list(range(logits.shape[0])):
-                    logits = logits[keep_rows].contiguous()
-                tokens = sampler.sample(logits, [states[i] for i in live])
                 entries, nxt = [], []
                 for i, tok in zip(live, tokens):
                     res = results[i]
@@ -128,13 +130,11 @@ def generate_requests(engine, sampler, prompts, n_predict: int = -1, stop_token_
                     elif engine.length(slots[i]) + 1 >= max_pos:
                         finish(i, "context")
                     else:
-                        entries.append(StepEntry(slots[i], [tok], [0]))
+                        entries.append((slots[i], tok, states[i]))
                         nxt.append(i)
                 live = nxt
-                if not live:
-                    break
-                logits = engine.step(entries)
-                rows = list(range(len(live)))
+                if live:
+                    tokens = decoder.step(entries)
         finally:
             for s in slots.values():
                 engine.free_slot(s)

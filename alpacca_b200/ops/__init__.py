@@ -343,11 +343,12 @@ def repeat_penalty(logits, recent, penalty):
     return logits
 
 
-def sample(logits, out, temperature, top_k, top_p, seed, streams, steps):
+def sample(logits, out, temperature, top_k, top_p, seed, streams, steps, seed_dev=None):
     """One token per row of float32 logits [B,V] into out int32 [B].
 
     temperature <= 0: first index of the maximum.  Else top_k (<= 0: all), top_p
-    (>= 1: all), and a draw with Philox(seed; stream, step) per row.
+    (>= 1: all), and a draw with Philox(seed; stream, step) per row.  `seed_dev` (int32 [2]: low
+    and high word, on the device) replaces `seed` when given.
     """
     _cuda(logits, out, streams, steps)
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(),
@@ -356,7 +357,31 @@ def sample(logits, out, temperature, top_k, top_p, seed, streams, steps):
     _i32(out, B, "out")
     _i32(streams, B, "streams")
     _i32(steps, B, "steps")
+    if seed_dev is not None:
+        _cuda(seed_dev)
+        _i32(seed_dev, 2, "seed_dev")
     _check(_lib("sampling").ab_sample(_p(logits), B, V, _p(out), ctypes.c_float(temperature), int(top_k),
                                       ctypes.c_float(top_p), ctypes.c_uint64(int(seed) & (2**64 - 1)),
-                                      _p(streams), _p(steps), _stream()), "sample")
+                                      _p(seed_dev), _p(streams), _p(steps), _stream()), "sample")
     return out
+
+
+def decode_advance(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, recent_pos, window,
+                   history, counter, n_rows):
+    """Feeds the sampled tokens back as the next step's inputs (all int32, on the device); see the kernel."""
+    _cuda(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, recent_pos, history, counter)
+    for t, name in ((tokens, "tokens"), (tok_pos, "tok_pos"), (kv_len, "kv_len"), (rng_step, "rng_step"),
+                    (tok_seq, "tok_seq"), (sampled, "sampled")):
+        _i32(t, n_rows, name)
+    hist_len = 0
+    if history is not None:
+        _need(history.dtype == torch.int32 and history.is_contiguous() and history.shape[1] == n_rows
+              and counter is not None and counter.dtype == torch.int32, "decode_advance: history int32 [L, rows]")
+        hist_len = history.shape[0]
+    if recent is not None:
+        _need(recent.dtype == torch.int32 and recent.is_contiguous() and recent.numel() >= n_rows * window
+              and recent_pos is not None, "decode_advance: recent int32 [rows, window]")
+        _i32(recent_pos, n_rows, "recent_pos")
+    _check(_lib("elementwise").ab_decode_advance(
+        _p(tokens), _p(tok_pos), _p(kv_len), _p(rng_step), _p(tok_seq), _p(sampled), _p(recent), _p(recent_pos),
+        int(window), _p(history), _p(counter), hist_len, n_rows, _stream()), "decode_advance")

@@ -26,9 +26,10 @@ def margin_ok(model_dir, prompt, tokens, tol):
     return True
 
 
+@pytest.mark.parametrize("graphs", [True, False])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["a", "b"])
-def test_greedy_generation_of_an_unequal_batch(model_dirs, name, dtype):
+def test_greedy_generation_of_an_unequal_batch(model_dirs, name, dtype, graphs):
     from alpacca_b200.api import Model, generate
     from alpacca_b200.sampling import SamplerParams
     d = model_dirs[(name, dtype)]
@@ -36,6 +37,8 @@ def test_greedy_generation_of_an_unequal_batch(model_dirs, name, dtype):
     lens = (5, 11, 17) if name == "a" else (1, 9, 33, 70)
     prompts = [tiny.prompt_tokens(cfg, n, 700 + i) for i, n in enumerate(lens)]
     model = Model.load(d, dtype=dtype, max_batch=4)
+    assert model.use_graphs, "the Llama model's decode steps are captured in CUDA graphs"
+    model.use_graphs = graphs
     res = generate(model, prompts, SamplerParams.greedy(), n_predict=8, stop_token_ids=[])
     stops = set(model.decoder.spec.stop_token_ids)
     for p, r in zip(prompts, res):
@@ -68,12 +71,14 @@ def test_stop_token_and_context_end_sequences(model_dirs):
     assert len(p) + full.tokens <= 16 and full.finish_reason in ("context", "length", "stop")
 
 
-def test_temperature_sampling_is_seeded_and_batch_independent(model_dirs):
+@pytest.mark.parametrize("graphs", [True, False])
+def test_temperature_sampling_is_seeded_and_batch_independent(model_dirs, graphs):
     from alpacca_b200.api import Model, generate
     from alpacca_b200.sampling import SamplerParams
     d = model_dirs[("b", "float32")]
     prompts = [tiny.prompt_tokens(tiny.TINY_B, n, 720 + i) for i, n in enumerate((1, 9, 33, 70))]
     model = Model.load(d, dtype="float32", max_batch=4)
+    model.use_graphs = graphs
     params = SamplerParams(temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=11)
     a = generate(model, prompts, params, n_predict=12, stop_token_ids=[])
     b = generate(model, prompts, params, n_predict=12, stop_token_ids=[])
@@ -118,3 +123,22 @@ def test_command_line(model_dirs):
     bad = subprocess.run([sys.executable, "-m", "alpacca_b200", "run", str(d), "hello"], cwd=ROOT,
                          capture_output=True, text=True, timeout=600)
     assert bad.returncode == 1 and "alpacca_b200: error:" in bad.stderr
+
+
+def test_graph_and_eager_decoding_agree_over_many_steps(model_dirs):
+    """Long generation with the reference's default sampler options (top-k, top-p, repeat penalty):
+    decode steps replayed from CUDA graphs give the tokens of the step-by-step path, across page
+    boundaries, while sequences end at different times."""
+    from alpacca_b200.api import Model, generate
+    from alpacca_b200.sampling import SamplerParams
+    d = model_dirs[("c", "float32")]
+    prompts = [tiny.prompt_tokens(tiny.TINY_C, n, 750 + i) for i, n in enumerate((3, 60, 130, 17, 64))]
+    model = Model.load(d, dtype="float32", max_batch=5)
+    out = {}
+    for graphs in (True, False):
+        model.use_graphs = graphs
+        res = generate(model, prompts, SamplerParams(seed=5), n_predict=150, stop_token_ids=[17, 400, 901])
+        out[graphs] = [(r.token_ids, r.finish_reason) for r in res]
+        assert model.engine.cache.slots.n_held == 0
+    assert out[True] == out[False]
+    assert len({len(t) for t, _ in out[True]}) > 1, "the sequences should end at different times"
