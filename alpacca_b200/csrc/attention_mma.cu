@@ -12,14 +12,16 @@
 //            single tokens; the host lists the tiles.
 //   decode   one new token per sequence: one CTA per (sequence, KV head, chunk
 //            of keys); each warp takes one page of the chunk, the warps'
-//            results are merged in shared memory, the chunks' in a second
-//            kernel, always in chunk order (the result does not depend on
-//            which CTA finishes first).
+//            results are merged in shared memory.  The chunks' partial results
+//            go to scratch memory, and the CTA that finishes last for its
+//            (sequence, KV head) merges them, always in chunk order, so the
+//            result does not depend on which CTA that is.
 //
 // Scores: (q.k) * scale; key s is seen by a token at position p iff
 // lo <= s <= p, lo = max(0, p - window + 1) (window 0: all)
 // (alpacca/model.py:447-467).  Head sizes: multiples of 16 up to 256.
 #include "common.cuh"
+#include "launch.cuh"
 #include <cuda_pipeline.h>
 
 #define PAGE 64
@@ -195,6 +197,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
   bf16* kbuf = qs + 64 * pitch;                            // [2][64][pitch]
   bf16* vbuf = kbuf + 2 * 64 * pitch;                      // [2][64][pitch]
 
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
@@ -282,7 +286,7 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
 template <int DMAX, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
-                        float* __restrict__ part_o, float* __restrict__ part_ml,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ arrivals,
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
                         const int* __restrict__ kv_len, int H, int K, int D, float scale_log2, int window,
@@ -292,6 +296,8 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][pitch]
   bf16* kv = qs + 16 * pitch;                                   // [NWARPS][2][64][pitch]
 
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
@@ -389,30 +395,37 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
       if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
     }
   }
-}
+  if (single) return;
 
-// merges the chunks of one (token, head) in chunk order
-__global__ void attention_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
-                                              const float* __restrict__ part_ml, const int* __restrict__ tok_seq,
-                                              const int* __restrict__ kv_len, int H, int D, int window,
-                                              int keys_per_chunk, int n_chunks) {
-  const int tok = blockIdx.x, h = blockIdx.y;
-  const int b = tok_seq[tok];
-  if (b < 0) return;
-  const int pos = kv_len[b] - 1;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int first = lo / keys_per_chunk, last = pos / keys_per_chunk;
-  if (first == last) return;            // the decode kernel wrote the result itself
-  const size_t base = ((size_t)tok * H + h) * n_chunks;
-  float m = -INFINITY;
-  for (int c = first; c <= last; ++c) m = fmaxf(m, part_ml[(base + c) * 2]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  // The last CTA to arrive for this (token, KV head, row tile) merges the chunks.  Each CTA
+  // publishes its partials (fence), then counts itself; the one that sees all others has, by the
+  // fence on the other side, their partials in view.  It puts the counter back to zero for the
+  // next launch.
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int n_active = last_chunk - first_chunk + 1;
+    int* counter = arrivals + (size_t)tok * gridDim.y + blockIdx.y;
+    const int seen = atomicAdd(counter, 1);
+    is_last = (seen == n_active - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = tid; idx < n_rows * D; idx += NWARPS * 32) {
+    const int r = idx / D, d = idx - r * D;
+    const int h = kh * G + rt * 16 + r;
+    const size_t base = ((size_t)tok * H + h) * n_chunks;
+    float m = -INFINITY;
+    for (int c = first_chunk; c <= last_chunk; ++c) m = fmaxf(m, __ldcg(part_ml + (base + c) * 2));
     float l = 0.f, o = 0.f;
-    for (int c = first; c <= last; ++c) {
-      const float mc = part_ml[(base + c) * 2];
+    for (int c = first_chunk; c <= last_chunk; ++c) {
+      const float mc = __ldcg(part_ml + (base + c) * 2);
       const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - m);
-      l += part_ml[(base + c) * 2 + 1] * f;
-      o += part_o[(base + c) * D + d] * f;
+      l += __ldcg(part_ml + (base + c) * 2 + 1) * f;
+      o += __ldcg(part_o + (base + c) * D + d) * f;
     }
     out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
   }
@@ -444,7 +457,7 @@ AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, c
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DM>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          (int)smem);                                                               \
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
-    attention_prefill_kernel<DM><<<grid, 128, smem, stream>>>(                                                     \
+    ab_launch(attention_prefill_kernel<DM>, grid, dim3(128), smem, stream,                                         \
         (const bf16*)qkv, q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages, block_table,           \
         table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, D, sl, window, tokens_per_tile);                      \
   }
@@ -457,8 +470,11 @@ AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, c
   return ab_launch_status();
 }
 
+// Scratch (only touched when n_chunks > 1): part_o float [n_tokens * H * n_chunks, D], part_ml float
+// [n_tokens * H * n_chunks, 2], arrivals int [n_tokens * K * ceil(G / 16)], which must be zero before
+// the first launch and is left zero by every launch.
 AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
-                                    const void* k_pages, const void* v_pages, const int* block_table,
+                                    int* arrivals, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
                                     int K, int D, float scale, int window, int n_chunks, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
@@ -476,20 +492,16 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DM, NW>,                                           \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
-    attention_decode_kernel<DM, NW><<<grid, NW * 32, smem, stream>>>(                                               \
-        (const bf16*)qkv, q_stride, (bf16*)out, part_o, part_ml, (const bf16*)k_pages, (const bf16*)v_pages,        \
-        block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, n_chunks);                                  \
+    ab_launch(attention_decode_kernel<DM, NW>, grid, dim3(NW * 32), smem, stream,                                   \
+        (const bf16*)qkv, q_stride, (bf16*)out, part_o, part_ml, arrivals, (const bf16*)k_pages,                    \
+        (const bf16*)v_pages, block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, n_chunks);            \
   }
-  int keys_per_chunk;
+  if (n_chunks > 1 && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
   switch (dmax_of(D)) {
-    case 64: AB_GO(64, 4); keys_per_chunk = 4 * PAGE; break;
-    case 128: AB_GO(128, 4); keys_per_chunk = 4 * PAGE; break;
-    default: AB_GO(256, 2); keys_per_chunk = 2 * PAGE; break;
+    case 64: AB_GO(64, 4); break;
+    case 128: AB_GO(128, 4); break;
+    default: AB_GO(256, 2); break;
   }
 #undef AB_GO
-  int rc = ab_launch_status();
-  if (rc != AB_OK || n_chunks == 1) return rc;
-  attention_decode_merge_kernel<<<dim3(n_tokens, H), 64, 0, stream>>>((bf16*)out, part_o, part_ml, tok_seq, kv_len,
-                                                                      H, D, window, keys_per_chunk, n_chunks);
   return ab_launch_status();
 }

@@ -6,6 +6,7 @@
 // T is the storage type of activations, weights and cache (float or bfloat16).
 // The residual stream itself is always float.
 #include "common.cuh"
+#include "launch.cuh"
 
 // ---------------------------------------------------------------------------
 // x[t,:] = table[token[t],:]   (alpacca/model.py:482; no scaling)
@@ -14,6 +15,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                   float* __restrict__ out, int n_rows, int width, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   if (row >= n_rows) return;
   const int tok = tokens[row];
@@ -31,9 +34,9 @@ AB_API int ab_embed_rows(const void* table, int dtype, const int* tokens, float*
   if (n_rows <= 0) return AB_OK;
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == AB_F32)
-    embed_rows_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)table, tokens, out, n_rows, width, vocab);
+    ab_launch(embed_rows_kernel<float>, n_rows, threads, 0, stream, (const float*)table, tokens, out, n_rows, width, vocab);
   else if (dtype == AB_BF16)
-    embed_rows_kernel<bf16><<<n_rows, threads, 0, stream>>>((const bf16*)table, tokens, out, n_rows, width, vocab);
+    ab_launch(embed_rows_kernel<bf16>, n_rows, threads, 0, stream, (const bf16*)table, tokens, out, n_rows, width, vocab);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
@@ -52,6 +55,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int n_out, int width, float eps) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int i_out = blockIdx.x;
   if (i_out >= n_out) return;
   const int src = rows ? rows[i_out] : i_out;
@@ -78,16 +83,98 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
   }
 }
 
+// The same with 4 elements per access, for widths that are multiples of 4.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  float4 v;
+  __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+  __device__ __forceinline__ float get(int i) const { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+  __device__ __forceinline__ void set(float a, float b, float c, float d) { v = make_float4(a, b, c, d); }
+};
+template <> struct Vec4<bf16> {
+  uint2 v;
+  __device__ __forceinline__ void load(const bf16* p) { v = *reinterpret_cast<const uint2*>(p); }
+  __device__ __forceinline__ void store(bf16* p) const { *reinterpret_cast<uint2*>(p) = v; }
+  __device__ __forceinline__ float get(int i) const {
+    const uint32_t w = i < 2 ? v.x : v.y;
+    return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+  }
+  __device__ __forceinline__ void set(float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+  }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                        const float* __restrict__ weight, T* __restrict__ out,
+                                        const int* __restrict__ rows, int n_out, int width, float eps) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int i_out = blockIdx.x;
+  if (i_out >= n_out) return;
+  const int src = rows ? rows[i_out] : i_out;
+  float* r = residual + (size_t)src * width;
+  const T* d = delta ? delta + (size_t)src * width : nullptr;
+  const bool write_back = (d != nullptr) && (rows == nullptr);
+  float ss = 0.f;
+  // the order of the sum depends on the width and the block size only
+  for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(r + i);
+    if (d) {
+      Vec4<T> dv;
+      dv.load(d + i);
+      v.x += dv.get(0); v.y += dv.get(1); v.z += dv.get(2); v.w += dv.get(3);
+      if (write_back) *reinterpret_cast<float4*>(r + i) = v;
+    }
+    ss += v.x * v.x;
+    ss += v.y * v.y;
+    ss += v.z * v.z;
+    ss += v.w * v.w;
+  }
+  ss = block_sum(ss, scratch);
+  if (out == nullptr) return;
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  T* o = out + (size_t)i_out * width;
+  for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(r + i);
+    if (d && !write_back) {
+      Vec4<T> dv;
+      dv.load(d + i);
+      v.x += dv.get(0); v.y += dv.get(1); v.z += dv.get(2); v.w += dv.get(3);
+    }
+    const float4 w = *reinterpret_cast<const float4*>(weight + i);
+    Vec4<T> ov;
+    ov.set((v.x * inv) * w.x, (v.y * inv) * w.y, (v.z * inv) * w.z, (v.w * inv) * w.w);
+    ov.store(o + i);
+  }
+}
+
 AB_API int ab_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, int dtype,
                           const int* rows, int n_out, int width, float eps, cudaStream_t stream) {
   if (n_out <= 0) return AB_OK;
+  if (width % 4 == 0) {
+    const int vthreads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+    if (dtype == AB_F32)
+      ab_launch(add_rmsnorm_vec4_kernel<float>, n_out, vthreads, 0, stream, residual, (const float*)delta, weight,
+                (float*)out, rows, n_out, width, eps);
+    else if (dtype == AB_BF16)
+      ab_launch(add_rmsnorm_vec4_kernel<bf16>, n_out, vthreads, 0, stream, residual, (const bf16*)delta, weight,
+                (bf16*)out, rows, n_out, width, eps);
+    else
+      return AB_BAD_ARG;
+    return ab_launch_status();
+  }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   if (dtype == AB_F32)
-    add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>(residual, (const float*)delta, weight, (float*)out,
-                                                             rows, n_out, width, eps);
+    ab_launch(add_rmsnorm_kernel<float>, n_out, threads, 0, stream, residual, (const float*)delta, weight,
+              (float*)out, rows, n_out, width, eps);
   else if (dtype == AB_BF16)
-    add_rmsnorm_kernel<bf16><<<n_out, threads, 0, stream>>>(residual, (const bf16*)delta, weight, (bf16*)out,
-                                                            rows, n_out, width, eps);
+    ab_launch(add_rmsnorm_kernel<bf16>, n_out, threads, 0, stream, residual, (const bf16*)delta, weight,
+              (bf16*)out, rows, n_out, width, eps);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
@@ -98,6 +185,8 @@ AB_API int ab_add_rmsnorm(float* residual, const void* delta, const float* weigh
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, size_t total, int width) {
+  pdl_trigger();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   y[i] = from_f32<T>(to_f32(y[i]) + bias[i % width]);
@@ -108,9 +197,9 @@ AB_API int ab_add_bias(void* y, int dtype, const float* bias, int n_rows, int wi
   if (total == 0) return AB_OK;
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == AB_F32)
-    add_bias_kernel<float><<<blocks, 256, 0, stream>>>((float*)y, bias, total, width);
+    ab_launch(add_bias_kernel<float>, blocks, 256, 0, stream, (float*)y, bias, total, width);
   else if (dtype == AB_BF16)
-    add_bias_kernel<bf16><<<blocks, 256, 0, stream>>>((bf16*)y, bias, total, width);
+    ab_launch(add_bias_kernel<bf16>, blocks, 256, 0, stream, (bf16*)y, bias, total, width);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
@@ -137,6 +226,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float* __restrict_
                                    int table_width, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                    int n_tokens, int H, int K, int D, int n_rot, int pairing, int page_size,
                                    int write_cache) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   if (t >= n_tokens) return;
   const int b = tok_seq[t];
@@ -194,11 +285,11 @@ AB_API int ab_rope_append(void* qkv, int dtype, const float* cos_t, const float*
   const int units = (H + 2 * K) * (D / 2);
   const int threads = units >= 1024 ? 256 : 128;
   if (dtype == AB_F32)
-    rope_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
+    ab_launch(rope_append_kernel<float>, n_tokens, threads, 0, stream,
         (float*)qkv, cos_t, sin_t, tok_pos, tok_seq, block_table, table_width, (float*)k_pages, (float*)v_pages,
         n_tokens, H, K, D, n_rot, pairing, page_size, write_cache);
   else if (dtype == AB_BF16)
-    rope_append_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
+    ab_launch(rope_append_kernel<bf16>, n_tokens, threads, 0, stream,
         (bf16*)qkv, cos_t, sin_t, tok_pos, tok_seq, block_table, table_width, (bf16*)k_pages, (bf16*)v_pages,
         n_tokens, H, K, D, n_rot, pairing, page_size, write_cache);
   else
@@ -215,6 +306,8 @@ AB_API int ab_rope_append(void* qkv, int dtype, const float* cos_t, const float*
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, size_t total, int F) {
+  pdl_trigger();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / F;
@@ -226,15 +319,44 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, siz
   act[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// bfloat16, 8 outputs per thread: one 16-byte piece of gate, one of up, one of output
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ act, size_t n_units, int units_per_row) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // unit = 8 outputs
+  if (u >= n_units) return;
+  const size_t t = u / units_per_row;
+  const int q = (int)(u - t * units_per_row);
+  const bf16* src = gu + (t * units_per_row + q) * 16;
+  const uint4 g4 = *reinterpret_cast<const uint4*>(src);
+  const uint4 u4 = *reinterpret_cast<const uint4*>(src + 8);
+  const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float g0 = __uint_as_float(gw[i] << 16), g1 = __uint_as_float(gw[i] & 0xffff0000u);
+    const float u0 = __uint_as_float(uw[i] << 16), u1 = __uint_as_float(uw[i] & 0xffff0000u);
+    __nv_bfloat162 r = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+    ow[i] = *reinterpret_cast<uint32_t*>(&r);
+  }
+  *reinterpret_cast<uint4*>(act + u * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 AB_API int ab_swiglu(const void* gu, void* act, int dtype, int n_rows, int F, cudaStream_t stream) {
   size_t total = (size_t)n_rows * F;
   if (total == 0) return AB_OK;
   if (F % 8) return AB_BAD_ARG;
+  if (dtype == AB_BF16) {
+    const size_t n_units = total / 8;
+    ab_launch(swiglu_bf16x8_kernel, (unsigned)((n_units + 255) / 256), 256, 0, stream, (const bf16*)gu, (bf16*)act,
+              n_units, F / 8);
+    return ab_launch_status();
+  }
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == AB_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)act, total, F);
+    ab_launch(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)act, total, F);
   else if (dtype == AB_BF16)
-    swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)act, total, F);
+    ab_launch(swiglu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)act, total, F);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
@@ -253,6 +375,8 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
                                       const int* __restrict__ sampled, int* __restrict__ recent,
                                       int* __restrict__ recent_pos, int window, int* __restrict__ history,
                                       int* __restrict__ counter, int history_len, int n_rows) {
+  pdl_trigger();
+  pdl_wait();
   const int slot = history ? (*counter % history_len) : 0;
   for (int b = threadIdx.x; b < n_rows; b += blockDim.x) {
     const int tok = sampled[b];
@@ -276,7 +400,7 @@ AB_API int ab_decode_advance(int* tokens, int* tok_pos, int* kv_len, int* rng_st
                              const int* sampled, int* recent, int* recent_pos, int window, int* history,
                              int* counter, int history_len, int n_rows, cudaStream_t stream) {
   if (n_rows <= 0) return AB_OK;
-  decode_advance_kernel<<<1, 256, 0, stream>>>(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent,
+  ab_launch(decode_advance_kernel, 1, 256, 0, stream, tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent,
                                                recent_pos, window, history, counter, history_len, n_rows);
   return ab_launch_status();
 }

@@ -19,6 +19,7 @@
 // gate, 16q+8..16q+15 up): act[m, 8q+g] = silu(gate) * up
 // (alpacca/model.py:513), so the activation costs no pass of its own.
 #include "common.cuh"
+#include "launch.cuh"
 
 #define GEMV_WARPS 8
 #define EPI_STORE_BF16 0
@@ -40,11 +41,21 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
+// activations were written by the kernel before this one: a plain (coherent) load, not the
+// read-only path, whose lines might have been fetched before the predecessor finished
+__device__ __forceinline__ uint4 ld_act(const bf16* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 template <int NT, int EPI>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias,
                  void* __restrict__ Y, int M, int N, int K, int ldy) {
   __shared__ float red[GEMV_WARPS][NT][32][4];
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -65,6 +76,9 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
   // warp w takes the k-groups w, w + 8, w + 16, ... (32 k each); 4 groups are in flight per thread
   constexpr int U = 4;
   const int n_groups = (K + 31) / 32;
+  // The weights do not depend on earlier kernels: the first loads of them go out before the
+  // wait for the predecessor, whose tail they overlap; the batch operand is read after it.
+  bool waited = false;
   for (int grp = warp; grp < n_groups; grp += GEMV_WARPS * U) {
     uint4 wl[U], wh[U], xv[U][NT];
 #pragma unroll
@@ -73,14 +87,17 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
       if (k < K) {           // K is a multiple of 8: a group of 8 lies inside or outside as a whole
         wl[u] = ldg_stream(w_lo + k);
         wh[u] = ldg_stream(w_hi + k);
-#pragma unroll
-        for (int i = 0; i < NT; ++i)
-          xv[u][i] = x_ok[i] ? __ldg(reinterpret_cast<const uint4*>(x_row[i] + k)) : make_uint4(0, 0, 0, 0);
       } else {
         wl[u] = wh[u] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int i = 0; i < NT; ++i) xv[u][i] = make_uint4(0, 0, 0, 0);
       }
+    }
+    if (!waited) { pdl_wait(); waited = true; }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = (grp + u * GEMV_WARPS) * 32 + t * 8;
+#pragma unroll
+      for (int i = 0; i < NT; ++i)
+        xv[u][i] = (k < K && x_ok[i]) ? ld_act(x_row[i] + k) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -92,6 +109,7 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
     }
   }
 
+  if (!waited) pdl_wait();
 #pragma unroll
   for (int i = 0; i < NT; ++i)
 #pragma unroll
@@ -141,7 +159,7 @@ static int launch(const void* X, const void* W, const float* bias, void* Y, int 
                   cudaStream_t stream) {
   const unsigned blocks = (unsigned)((N + 15) / 16);
   const int threads = GEMV_WARPS * 32;
-#define AB_GO(NT) gemv_bf16_kernel<NT, EPI><<<blocks, threads, 0, stream>>>((const bf16*)X, (const bf16*)W, bias, Y, M, N, K, ldy)
+#define AB_GO(NT) ab_launch(gemv_bf16_kernel<NT, EPI>, blocks, threads, 0, stream, (const bf16*)X, (const bf16*)W, bias, Y, M, N, K, ldy)
   if (M <= 8) AB_GO(1);
   else if (M <= 16) AB_GO(2);
   else AB_GO(4);

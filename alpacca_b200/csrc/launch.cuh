@@ -1,0 +1,47 @@
+// Launches with programmatic dependent launch: a kernel launched this way may
+// start while its predecessor in the stream is still running.  Every kernel of
+// this package follows one discipline, which makes that safe:
+//   - pdl_trigger() first: the next kernel in the stream may be scheduled as
+//     soon as every block of this one has started;
+//   - work that does not depend on earlier kernels (fetching weights) may come
+//     next;
+//   - pdl_wait() before the first read of anything an earlier kernel wrote and
+//     before the first write to global memory.  It returns when the
+//     predecessor has completed and its writes are visible.  Since every
+//     kernel waits before it completes, completion is transitive along the
+//     stream.
+// Decode steps are chains of many short kernels; overlapping each kernel's
+// launch and first memory round trip with its predecessor's tail is worth a
+// large part of the step time.  ALPACCA_B200_PDL=0 turns the attribute off
+// (the device-side instructions are then no-ops).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdlib.h>
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool ab_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("ALPACCA_B200_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ab_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ab_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -17,6 +17,7 @@
 // Weights are summed as 64-bit fixed point (w * 2^40), so every sum is exact
 // integer arithmetic and does not depend on the order of the additions.
 #include "common.cuh"
+#include "launch.cuh"
 
 #define SAMPLE_THREADS 1024
 #define W_SHIFT 40
@@ -28,6 +29,8 @@
 // ---------------------------------------------------------------------------
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, const int* __restrict__ recent, int window,
                                       int vocab, float penalty) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int* r = recent + (size_t)row * window;
   float* l = logits + (size_t)row * vocab;
@@ -46,7 +49,7 @@ __global__ void repeat_penalty_kernel(float* __restrict__ logits, const int* __r
 AB_API int ab_repeat_penalty(float* logits, const int* recent, int n_rows, int window, int vocab, float penalty,
                              cudaStream_t stream) {
   if (n_rows <= 0 || window <= 0) return AB_OK;
-  repeat_penalty_kernel<<<n_rows, 128, 0, stream>>>(logits, recent, window, vocab, penalty);
+  ab_launch(repeat_penalty_kernel, n_rows, 128, 0, stream, logits, recent, window, vocab, penalty);
   return ab_launch_status();
 }
 
@@ -138,6 +141,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
               float top_p, unsigned int seed_lo, unsigned int seed_hi, const unsigned int* __restrict__ seed_dev,
               const int* __restrict__ streams, const int* __restrict__ steps) {
   __shared__ SampleShared sh;
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* l = logits + (size_t)row * vocab;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -362,8 +367,7 @@ AB_API int ab_sample(const float* logits, int n_rows, int vocab, int* out, float
                      const int* steps, cudaStream_t stream) {
   if (n_rows <= 0) return AB_OK;
   if (vocab <= 0) return AB_BAD_ARG;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, out, temperature, top_k, top_p,
-                                                       (unsigned int)(seed & 0xffffffffull),
-                                                       (unsigned int)(seed >> 32), seed_dev, streams, steps);
+  ab_launch(sample_kernel, n_rows, SAMPLE_THREADS, 0, stream, logits, vocab, out, temperature, top_k, top_p,
+            (unsigned int)(seed & 0xffffffffull), (unsigned int)(seed >> 32), seed_dev, streams, steps);
   return ab_launch_status();
 }

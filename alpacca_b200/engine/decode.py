@@ -126,6 +126,7 @@ class GraphDecoder:
         self.layout: list = []          # slot of each row of the current shape
         self.row_of: dict = {}
         self.mask: list = []
+        self.expect: dict = {}          # slot -> (length, last sampled token) after the last step
         self.pages_seen = -1
 
     # -- the captured step -------------------------------------------------------------
@@ -219,7 +220,10 @@ class GraphDecoder:
         need_pages = max([len(grp.page_lists[slot]) for grp in cache.kv_groups for slot, _, _ in live] + [1])
         slots = [slot for slot, _, _ in live]
         sh = self.shape
-        keep = (sh is not None and all(s in self.row_of for s in slots) and sh.width >= need_pages
+        # the device state is only valid for sequences that went on exactly as the last step left them
+        fresh = all(self.expect.get(slot) in ((cache.length(slot), tok), (cache.length(slot), None))
+                    for slot, tok, _ in live)
+        keep = (sh is not None and fresh and all(s in self.row_of for s in slots) and sh.width >= need_pages
                 and bucket_rows(len(slots)) * 2 > sh.rows)
         if not keep:
             key = (bucket_rows(len(live)), _width_bucket(need_pages))
@@ -272,7 +276,9 @@ class GraphDecoder:
         rows = self._prepare(live, steps, always_mask)
         for _ in range(steps):
             self.shape.graph.replay()
-        self.engine.cache.commit([(slot, steps) for slot, _, _ in live])
+        cache = self.engine.cache
+        cache.commit([(slot, steps) for slot, _, _ in live])
+        self.expect = {slot: (cache.length(slot), None) for slot, _, _ in live}
         return rows
 
     def step(self, live):
@@ -284,9 +290,10 @@ class GraphDecoder:
         torch.cuda.current_stream().synchronize()
         got = sh.sampled_host.tolist()
         tokens = [got[r] for r in rows]
-        for (_, _, st), t in zip(live, tokens):
+        for (slot, _, st), t in zip(live, tokens):
             st.step += 1
             st.accept(t)
+            self.expect[slot] = (self.expect[slot][0], t)
         return tokens
 
     def history(self, n_steps: int, n_live: int) -> torch.Tensor:
@@ -302,6 +309,7 @@ class GraphDecoder:
         if sampler is not None:
             self.sampler = sampler
         self.shape, self.layout, self.row_of, self.mask, self.pages_seen = None, [], {}, [], -1
+        self.expect = {}
 
     def close(self):
         self.shapes.clear()

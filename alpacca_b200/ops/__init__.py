@@ -260,6 +260,23 @@ def _prefill_tiles(ctx, G, device):
     return plan
 
 
+_ARRIVALS: dict = {}
+
+
+def _arrival_counters(device, n: int):
+    """Zeroed int32 counters for the decode kernel's last-arrival merge.  Every launch leaves them
+    zero again, so one buffer per device serves all launches (which run one after another in a
+    stream).  It only grows outside a graph capture."""
+    buf = _ARRIVALS.get(device)
+    if buf is None or buf.numel() < n:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError(f"attention: {n} arrival counters needed during graph capture, "
+                              f"{0 if buf is None else buf.numel()} allocated before it")
+        buf = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _ARRIVALS[device] = buf
+    return buf
+
+
 def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
     """Tensor-core attention (bfloat16) over the paged cache; prefill or decode by the step's kind."""
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
@@ -280,12 +297,14 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
         if n_chunks > 1:
             part_o = torch.empty((T * H * n_chunks, D), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((T * H * n_chunks, 2), dtype=torch.float32, device=qkv.device)
+            arrivals = _arrival_counters(qkv.device, T * K * (-(-(H // K) // 16)))
         else:
-            part_o = part_ml = None
+            part_o = part_ml = arrivals = None
         _i32(ctx.tok_seq, T, "tok_seq")
         _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
         _check(lib.ab_attention_decode_bf16(
-            _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(k_pages), _p(v_pages), _p(table),
+            _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(arrivals), _p(k_pages), _p(v_pages),
+            _p(table),
             table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0),
             n_chunks, _stream()), "attention_decode")
         return out

@@ -215,6 +215,16 @@ def run_ours(args):
     weights = model_bytes(model)
     kv_per_token = sum(g.bytes_per_token for g in model.engine.cache.kv_groups)
 
+    if args.only == "decode":
+        tps, ms_step, _, kernels = measure_decode(model, args.batch, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "tok_s": round(tps, 1),
+                          "ms_per_step": round(ms_step, 4), "kernels_per_step": kernels}))
+        return 0
+    if args.only == "prefill":
+        pre_ms = measure_prefill(model, runs=max(args.steps, 1))
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3)}))
+        return 0
+
     clocks = ClockSampler()
     clocks.start()
     tps, ms_step, ctx_mean, kernels = measure_decode(model, args.batch, args.steps, args.warmup)
@@ -354,6 +364,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     n = int(os.environ.get("WORLD_SIZE", args.gpus))
     if args.gpus > 1 or n > 1:

@@ -134,11 +134,16 @@ def test_graph_and_eager_decoding_agree_over_many_steps(model_dirs):
     d = model_dirs[("c", "float32")]
     prompts = [tiny.prompt_tokens(tiny.TINY_C, n, 750 + i) for i, n in enumerate((3, 60, 130, 17, 64))]
     model = Model.load(d, dtype="float32", max_batch=5)
+    params = SamplerParams(seed=5)
+    model.use_graphs = False
+    free = generate(model, prompts, params, n_predict=150, stop_token_ids=[])
+    stops = [free[0].token_ids[40], free[2].token_ids[90], free[4].token_ids[120]]
     out = {}
     for graphs in (True, False):
         model.use_graphs = graphs
-        res = generate(model, prompts, SamplerParams(seed=5), n_predict=150, stop_token_ids=[17, 400, 901])
+        res = generate(model, prompts, params, n_predict=150, stop_token_ids=stops)
         out[graphs] = [(r.token_ids, r.finish_reason) for r in res]
         assert model.engine.cache.slots.n_held == 0
     assert out[True] == out[False]
     assert len({len(t) for t, _ in out[True]}) > 1, "the sequences should end at different times"
+    assert out[False][1][0] == free[1].token_ids[:len(out[False][1][0])]
