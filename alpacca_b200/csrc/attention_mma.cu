@@ -197,8 +197,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
   bf16* kbuf = qs + 64 * pitch;                            // [2][64][pitch]
   bf16* vbuf = kbuf + 2 * 64 * pitch;                      // [2][64][pitch]
 
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
@@ -281,7 +281,9 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
 }
 
 // ---------------------------------------------------------------------------
-// decode: one token per sequence; grid (sequence, KV head x row tile, chunk)
+// decode: one token per sequence; grid (sequence, KV head x row tile, chunk).
+// A chunk is `pages_per_cta` pages; warp w of the CTA takes the chunk's pages
+// w, w + NWARPS, ... one after another.
 // ---------------------------------------------------------------------------
 template <int DMAX, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
@@ -290,14 +292,14 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
                         const int* __restrict__ kv_len, int H, int K, int D, float scale_log2, int window,
-                        int n_chunks) {
+                        int pages_per_cta, int n_chunks) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch = D + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][pitch]
   bf16* kv = qs + 16 * pitch;                                   // [NWARPS][2][64][pitch]
 
-  pdl_trigger();
-  pdl_wait();
+  // What this kernel reads before the wait was written in earlier steps (lengths, block table,
+  // every page but the one that holds this step's token), never by the kernels just before it.
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
@@ -305,16 +307,39 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
   const int tok = blockIdx.x;
   const int kh = blockIdx.y / row_tiles, rt = blockIdx.y - kh * row_tiles;
   const int chunk = blockIdx.z;
+  // In a decode step row `tok` of the batch is sequence `tok` (or padding: tok_seq < 0), so the
+  // sequence's length and its block-table entries are asked for together with the padding mark
+  // instead of one after the other.
+  const int* bt = block_table + (size_t)tok * table_width;
   const int b = tok_seq[tok];
-  if (b < 0) return;
-  const int len = kv_len[b];
+  const int len = kv_len[tok];
+  const int my_first = chunk * pages_per_cta + warp;
+  const int my_first_entry = my_first < table_width ? bt[my_first] : 0;
+  if (b < 0) { pdl_wait(); pdl_trigger(); return; }
   const int pos = len - 1;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int keys_per_chunk = NWARPS * PAGE;
-  const int first_chunk = lo / keys_per_chunk, last_chunk = pos / keys_per_chunk;
-  if (chunk < first_chunk || chunk > last_chunk) return;
+  const int first_page = lo / PAGE, last_page = pos / PAGE;
+  const int first_chunk = first_page / pages_per_cta, last_chunk = last_page / pages_per_cta;
+  if (chunk < first_chunk || chunk > last_chunk) { pdl_wait(); pdl_trigger(); return; }
   const int n_rows = min(16, G - rt * 16);
 
+  RowState<DMAX> st;
+  init_state(st);
+  bf16* ks = kv + (size_t)warp * 2 * 64 * pitch;
+  bf16* vs = ks + 64 * pitch;
+  const int page_begin = max(chunk * pages_per_cta, first_page);
+  const int page_end = min((chunk + 1) * pages_per_cta, last_page + 1);
+  int page = page_begin + warp;
+  // the first page of this warp, unless it is the one being written right now, is fetched before the wait
+  const bool early = page < page_end && page != last_page;
+  if (early) {
+    const size_t base = ((size_t)(page == my_first ? my_first_entry : bt[page]) * K + kh) * PAGE * D;
+    load_tile_async(ks, k_pages + base, D, pitch, lane, 32);
+    load_tile_async(vs, v_pages + base, D, pitch, lane, 32);
+    cp_async_commit();
+  }
+  pdl_wait();
+  pdl_trigger();
   {
     const int cpr = D >> 3;
     for (int c = tid; c < 16 * cpr; c += NWARPS * 32) {
@@ -325,24 +350,20 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
       *reinterpret_cast<uint4*>(qs + r * pitch + cc * 8) = v;
     }
   }
-  RowState<DMAX> st;
-  init_state(st);
-  const int page_idx = chunk * NWARPS + warp;
-  const int key0 = page_idx * PAGE;
-  const bool active = key0 <= pos && key0 + PAGE - 1 >= lo;
-  bf16* ks = kv + (size_t)warp * 2 * 64 * pitch;
-  bf16* vs = ks + 64 * pitch;
-  if (active) {
-    const size_t base = ((size_t)block_table[(size_t)b * table_width + page_idx] * K + kh) * PAGE * D;
-    load_tile_async(ks, k_pages + base, D, pitch, lane, 32);
-    load_tile_async(vs, v_pages + base, D, pitch, lane, 32);
-  }
-  cp_async_commit();
-  cp_async_wait<0>();
   __syncthreads();
-  if (active) {
+  for (bool first = true; page < page_end; page += NWARPS, first = false) {
+    if (!(first && early)) {
+      const size_t base = ((size_t)bt[page] * K + kh) * PAGE * D;
+      load_tile_async(ks, k_pages + base, D, pitch, lane, 32);
+      load_tile_async(vs, v_pages + base, D, pitch, lane, 32);
+      cp_async_commit();
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+    const int key0 = page * PAGE;
     const bool need_mask = (key0 + PAGE - 1 > pos) || (key0 < lo);
     attend_tile<DMAX>(st, qs, ks, vs, pitch, D, scale_log2, key0, pos, pos, lo, lo, need_mask);
+    __syncwarp();      // every lane is done reading the tile before the next one overwrites it
   }
   float l0 = st.l[0], l1 = st.l[1];
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -436,8 +457,8 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
 // ---------------------------------------------------------------------------
 static int dmax_of(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : 256); }
 
-// keys that one decode CTA covers, for head size D (the caller sizes the scratch with it)
-AB_API int ab_attention_decode_chunk(int D) { return (dmax_of(D) == 256 ? 2 : 4) * PAGE; }
+// warps of a decode CTA for head size D: a CTA takes a multiple of this many pages
+AB_API int ab_attention_decode_warps(int D) { return dmax_of(D) == 64 ? 8 : (dmax_of(D) == 128 ? 4 : 2); }
 
 AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
                                      const void* v_pages, const int* block_table, int table_width,
@@ -476,9 +497,12 @@ AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, c
 AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
                                     int* arrivals, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
-                                    int K, int D, float scale, int window, int n_chunks, cudaStream_t stream) {
+                                    int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
+                                    cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
-  if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535) return AB_BAD_ARG;
+  if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535 || pages_per_cta < 1)
+    return AB_BAD_ARG;
+  if ((long long)pages_per_cta * n_chunks < table_width) return AB_BAD_ARG;   // the chunks must cover the table
   const int G = H / K, row_tiles = (G + 15) / 16;
   if ((long long)K * row_tiles > 65535) return AB_BAD_ARG;
   const int pitch = D + 8;
@@ -494,11 +518,12 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
     ab_launch(attention_decode_kernel<DM, NW>, grid, dim3(NW * 32), smem, stream,                                   \
         (const bf16*)qkv, q_stride, (bf16*)out, part_o, part_ml, arrivals, (const bf16*)k_pages,                    \
-        (const bf16*)v_pages, block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, n_chunks);            \
+        (const bf16*)v_pages, block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, pages_per_cta,        \
+        n_chunks);                                                                                                  \
   }
   if (n_chunks > 1 && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
   switch (dmax_of(D)) {
-    case 64: AB_GO(64, 4); break;
+    case 64: AB_GO(64, 8); break;
     case 128: AB_GO(128, 4); break;
     default: AB_GO(256, 2); break;
   }

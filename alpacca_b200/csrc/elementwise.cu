@@ -15,8 +15,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                   float* __restrict__ out, int n_rows, int width, int vocab) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   if (row >= n_rows) return;
   const int tok = tokens[row];
@@ -55,8 +55,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int n_out, int width, float eps) {
   __shared__ float scratch[32];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int i_out = blockIdx.x;
   if (i_out >= n_out) return;
   const int src = rows ? rows[i_out] : i_out;
@@ -112,8 +112,8 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const T* _
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int n_out, int width, float eps) {
   __shared__ float scratch[32];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int i_out = blockIdx.x;
   if (i_out >= n_out) return;
   const int src = rows ? rows[i_out] : i_out;
@@ -185,8 +185,8 @@ AB_API int ab_add_rmsnorm(float* residual, const void* delta, const float* weigh
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, size_t total, int width) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   y[i] = from_f32<T>(to_f32(y[i]) + bias[i % width]);
@@ -226,8 +226,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float* __restrict_
                                    int table_width, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                    int n_tokens, int H, int K, int D, int n_rot, int pairing, int page_size,
                                    int write_cache) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   if (t >= n_tokens) return;
   const int b = tok_seq[t];
@@ -276,12 +276,128 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float* __restrict_
   }
 }
 
+// 8 consecutive elements to and from float registers
+__device__ __forceinline__ void load8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float* v) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 r = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&r);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// The same for head sizes and rotated sizes that are multiples of 16: one thread per unit of 16
+// elements of a head (two pieces of 8), 16-byte accesses throughout.  A rotated unit u covers the
+// pairs 8u .. 8u+7 of its head: with pairing 0 the 16 consecutive elements from 16u (even places a,
+// odd places b), with pairing 1 the pieces at 8u and n_rot/2 + 8u.
+template <typename T>
+__global__ void rope_append_vec_kernel(T* __restrict__ qkv, const float* __restrict__ cos_t,
+                                       const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
+                                       const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                       int table_width, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                       int n_tokens, int H, int K, int D, int n_rot, int pairing, int page_size,
+                                       int write_cache) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const int b = tok_seq[t];
+  if (b < 0) return;
+  const int pos = tok_pos[t];
+  const int upp = D >> 4, rot_units = n_rot >> 4, half_r = n_rot >> 1;
+  const int n_heads = H + 2 * K;
+  T* row = qkv + (size_t)t * n_heads * D;
+  const int page = block_table[(size_t)b * table_width + pos / page_size];
+  const int off = pos % page_size;
+  for (int unit = blockIdx.y * blockDim.x + threadIdx.x; unit < n_heads * upp; unit += gridDim.y * blockDim.x) {
+    const int head = unit / upp, u = unit - head * upp;
+    T* x = row + (size_t)head * D;
+    const bool rotate = head < H + K && cos_t != nullptr && u < rot_units;
+    int ia, ib;                       // first elements of the unit's two pieces
+    if (rotate && pairing == 1) { ia = 8 * u; ib = half_r + 8 * u; }
+    else if (rotate) { ia = 16 * u; ib = ia + 8; }
+    else { ia = (head < H + K && cos_t != nullptr) ? n_rot + 16 * (u - rot_units) : 16 * u; ib = ia + 8; }
+    float va[8], vb[8];
+    load8(x + ia, va);
+    load8(x + ib, vb);
+    if (rotate) {
+      float c[8], sn[8];
+      load8(cos_t + (size_t)pos * half_r + 8 * u, c);
+      load8(sin_t + (size_t)pos * half_r + 8 * u, sn);
+      if (pairing == 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float x0 = va[j], x1 = vb[j];
+          va[j] = x0 * c[j] - x1 * sn[j];
+          vb[j] = x0 * sn[j] + x1 * c[j];
+        }
+      } else {
+        // pairs (2j, 2j+1) of the 16 consecutive elements: pair j lies in va for j < 4, in vb for j >= 4
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float* v = j < 4 ? va : vb;
+          const int e = 2 * (j & 3);
+          const float x0 = v[e], x1 = v[e + 1];
+          v[e] = x0 * c[j] - x1 * sn[j];
+          v[e + 1] = x0 * sn[j] + x1 * c[j];
+        }
+      }
+    }
+    if (head < H) {
+      store8(x + ia, va);
+      store8(x + ib, vb);
+    } else if (write_cache) {
+      const bool is_k = head < H + K;
+      const int kh = is_k ? head - H : head - H - K;
+      T* dst = (is_k ? k_pages : v_pages) + (((size_t)page * K + kh) * page_size + off) * D;
+      store8(dst + ia, va);
+      store8(dst + ib, vb);
+      if (is_k) {
+        store8(x + ia, va);
+        store8(x + ib, vb);
+      }
+    }
+  }
+}
+
 AB_API int ab_rope_append(void* qkv, int dtype, const float* cos_t, const float* sin_t, const int* tok_pos,
                           const int* tok_seq, const int* block_table, int table_width, void* k_pages,
                           void* v_pages, int n_tokens, int H, int K, int D, int n_rot, int pairing,
                           int page_size, int write_cache, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if ((D & 1) || (n_rot & 1) || n_rot > D || n_rot < 0) return AB_BAD_ARG;
+  if (D % 16 == 0 && n_rot % 16 == 0 && (dtype == AB_F32 || dtype == AB_BF16)) {
+    const int vunits = (H + 2 * K) * (D / 16);
+    const int vthreads = vunits >= 256 ? 256 : (vunits >= 128 ? 128 : 64);
+    const dim3 grid(n_tokens, n_tokens < 64 ? (vunits + vthreads - 1) / vthreads : 1);
+    if (dtype == AB_F32)
+      ab_launch(rope_append_vec_kernel<float>, grid, dim3(vthreads), 0, stream, (float*)qkv, cos_t, sin_t, tok_pos,
+                tok_seq, block_table, table_width, (float*)k_pages, (float*)v_pages, n_tokens, H, K, D, n_rot,
+                pairing, page_size, write_cache);
+    else
+      ab_launch(rope_append_vec_kernel<bf16>, grid, dim3(vthreads), 0, stream, (bf16*)qkv, cos_t, sin_t, tok_pos,
+                tok_seq, block_table, table_width, (bf16*)k_pages, (bf16*)v_pages, n_tokens, H, K, D, n_rot,
+                pairing, page_size, write_cache);
+    return ab_launch_status();
+  }
   const int units = (H + 2 * K) * (D / 2);
   const int threads = units >= 1024 ? 256 : 128;
   if (dtype == AB_F32)
@@ -306,8 +422,8 @@ AB_API int ab_rope_append(void* qkv, int dtype, const float* cos_t, const float*
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, size_t total, int F) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / F;
@@ -321,8 +437,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, siz
 
 // bfloat16, 8 outputs per thread: one 16-byte piece of gate, one of up, one of output
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ act, size_t n_units, int units_per_row) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // unit = 8 outputs
   if (u >= n_units) return;
   const size_t t = u / units_per_row;
@@ -375,8 +491,8 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
                                       const int* __restrict__ sampled, int* __restrict__ recent,
                                       int* __restrict__ recent_pos, int window, int* __restrict__ history,
                                       int* __restrict__ counter, int history_len, int n_rows) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int slot = history ? (*counter % history_len) : 0;
   for (int b = threadIdx.x; b < n_rows; b += blockDim.x) {
     const int tok = sampled[b];

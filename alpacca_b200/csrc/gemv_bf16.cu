@@ -5,9 +5,20 @@
 // tensor cores (mma.sync m16n8k16, float32 accumulation) with the weights as the
 // 16-row operand and the batch as the 8-column operand, so any M up to 8 costs
 // one instruction per 16 weight rows x 16 k, and M up to 32 two to four.
-// A CTA owns 16 weight rows; its 8 warps split K between them and their partial
-// sums are added in shared memory in warp order (a fixed order: the result of
-// a row does not depend on timing).
+//
+// The kernel is bound by memory latency, not arithmetic: what matters is how
+// many bytes are in flight.  A CTA owns 16 weight rows and one of S slices of K
+// (grid N/16 x S); its 8 warps split the slice into runs, and every thread issues the loads
+// of up to 8 k-groups (256 bytes) before it consumes any, so a CTA of a
+// 2048-wide slice has all its 64 KB in flight at once.  S is chosen by the host
+// so that even a matrix of few rows gives a few CTAs to every processor.  The
+// weights do not depend on earlier kernels, so their loads are issued before the
+// wait of programmatic dependent launch and overlap the predecessor's tail.
+//
+// Sums: the warps' partial sums are added in shared memory in warp order; with
+// S > 1 each CTA writes its tile of partial sums to scratch memory and the CTA
+// that arrives last for its 16 rows adds the S tiles in slice order and runs the
+// epilogue.  Both orders are fixed: a result does not depend on timing.
 //
 // k is permuted inside each group of 32 so that a thread's two 16-byte loads
 // (8 consecutive k of weight rows g and g+8) are its operand registers of two
@@ -22,6 +33,7 @@
 #include "launch.cuh"
 
 #define GEMV_WARPS 8
+#define GEMV_U 8
 #define EPI_STORE_BF16 0
 #define EPI_STORE_F32 1
 #define EPI_SWIGLU_BF16 2
@@ -50,15 +62,50 @@ __device__ __forceinline__ uint4 ld_act(const bf16* p) {
   return v;
 }
 
+template <int EPI>
+__device__ __forceinline__ void epilogue(const float c[4], int i, int ln, int n0, const float* __restrict__ bias,
+                                         void* __restrict__ Y, int M, int N, int ldy) {
+  const int gg = ln >> 2, tt = ln & 3;
+  const int m0 = i * 8 + 2 * tt;             // batch rows m0, m0 + 1
+  const int na = n0 + gg, nb = n0 + gg + 8;  // weight rows of c[0..1] and c[2..3]
+  if (EPI == EPI_SWIGLU_BF16) {
+    // na is a gate row, nb the up row of the same unit: output column (n0 / 16) * 8 + gg
+    if (na < N) {
+      const float bg = bias ? bias[na] : 0.f, bu = bias ? bias[nb] : 0.f;
+      const int col = (n0 >> 1) + gg;
+      bf16* y = reinterpret_cast<bf16*>(Y);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (m0 + j < M) {
+          const float gate = c[j] + bg, up = c[2 + j] + bu;
+          y[(size_t)(m0 + j) * ldy + col] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = (j < 2) ? na : nb, m = m0 + (j & 1);
+      if (n < N && m < M) {
+        const float v = c[j] + (bias ? bias[n] : 0.f);
+        if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(Y)[(size_t)m * ldy + n] = v;
+        else reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + n] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
 template <int NT, int EPI>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias,
-                 void* __restrict__ Y, int M, int N, int K, int ldy) {
+                 void* __restrict__ Y, float* __restrict__ partials, int* __restrict__ arrivals, int M, int N, int K,
+                 int ldy, int groups_per_slice) {
   __shared__ float red[GEMV_WARPS][NT][32][4];
-  pdl_trigger();
+  __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
+  const int S = gridDim.y, slice = blockIdx.y;
   // rows past N read row N-1 again; their sums are never stored
   const bf16* w_lo = W + (size_t)min(n0 + g, N - 1) * K;
   const bf16* w_hi = W + (size_t)min(n0 + g + 8, N - 1) * K;
@@ -73,93 +120,104 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
 #pragma unroll
   for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  // warp w takes the k-groups w, w + 8, w + 16, ... (32 k each); 4 groups are in flight per thread
-  constexpr int U = 4;
+  // this CTA's k-groups (32 k each): [slice_begin, slice_end); each warp takes a contiguous run of
+  // them, so that a thread's consecutive loads complete the 128-byte lines they touch
   const int n_groups = (K + 31) / 32;
-  // The weights do not depend on earlier kernels: the first loads of them go out before the
-  // wait for the predecessor, whose tail they overlap; the batch operand is read after it.
+  const int slice_begin = slice * groups_per_slice;
+  const int slice_end = min(n_groups, slice_begin + groups_per_slice);
+  const int per_warp = (slice_end - slice_begin + GEMV_WARPS - 1) / GEMV_WARPS;
+  const int grp_begin = slice_begin + warp * per_warp;
+  const int grp_end = min(slice_end, grp_begin + per_warp);
   bool waited = false;
-  for (int grp = warp; grp < n_groups; grp += GEMV_WARPS * U) {
-    uint4 wl[U], wh[U], xv[U][NT];
+  for (int grp = grp_begin; grp < grp_end; grp += GEMV_U) {
+    uint4 wl[GEMV_U], wh[GEMV_U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int k = (grp + u * GEMV_WARPS) * 32 + t * 8;
-      if (k < K) {           // K is a multiple of 8: a group of 8 lies inside or outside as a whole
+    for (int u = 0; u < GEMV_U; ++u) {
+      const int gi = grp + u;
+      const int k = gi * 32 + t * 8;
+      if (gi < grp_end && k < K) {   // K is a multiple of 8: a piece of 8 lies inside or outside as a whole
         wl[u] = ldg_stream(w_lo + k);
         wh[u] = ldg_stream(w_hi + k);
       } else {
         wl[u] = wh[u] = make_uint4(0, 0, 0, 0);
       }
     }
-    if (!waited) { pdl_wait(); waited = true; }
+    if (!waited) { pdl_wait(); pdl_trigger(); waited = true; }
+    // the batch operand, four k-groups at a time: loaded together, then consumed
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int k = (grp + u * GEMV_WARPS) * 32 + t * 8;
+    for (int u0 = 0; u0 < GEMV_U; u0 += 4) {
+      uint4 xv[4][NT];
 #pragma unroll
-      for (int i = 0; i < NT; ++i)
-        xv[u][i] = (k < K && x_ok[i]) ? ld_act(x_row[i] + k) : make_uint4(0, 0, 0, 0);
-    }
+      for (int u = 0; u < 4; ++u) {
+        const int gi = grp + u0 + u;
+        const int k = gi * 32 + t * 8;
+        const bool in = gi < grp_end && k < K;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+        for (int i = 0; i < NT; ++i) xv[u][i] = (in && x_ok[i]) ? ld_act(x_row[i] + k) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-      for (int i = 0; i < NT; ++i) {
-        mma_bf16_16816(acc[i], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][i].x, xv[u][i].y);
-        mma_bf16_16816(acc[i], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv[u][i].z, xv[u][i].w);
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          mma_bf16_16816(acc[i], wl[u0 + u].x, wh[u0 + u].x, wl[u0 + u].y, wh[u0 + u].y, xv[u][i].x, xv[u][i].y);
+          mma_bf16_16816(acc[i], wl[u0 + u].z, wh[u0 + u].z, wl[u0 + u].w, wh[u0 + u].w, xv[u][i].z, xv[u][i].w);
+        }
       }
     }
   }
+  if (!waited) { pdl_wait(); pdl_trigger(); }
 
-  if (!waited) pdl_wait();
 #pragma unroll
   for (int i = 0; i < NT; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) red[warp][i][lane][j] = acc[i][j];
   __syncthreads();
   // threads 0 .. NT*32-1 finish one (n-tile, lane) each
-  if (threadIdx.x < NT * 32) {
-    const int i = threadIdx.x >> 5, ln = threadIdx.x & 31;
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool finisher = threadIdx.x < NT * 32;
+  const int i = threadIdx.x >> 5, ln = threadIdx.x & 31;
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  if (finisher) {
 #pragma unroll
     for (int w = 0; w < GEMV_WARPS; ++w)
 #pragma unroll
       for (int j = 0; j < 4; ++j) c[j] += red[w][i][ln][j];
-    const int gg = ln >> 2, tt = ln & 3;
-    const int m0 = i * 8 + 2 * tt;          // batch rows m0, m0 + 1
-    const int na = n0 + gg, nb = n0 + gg + 8;  // weight rows of c[0..1] and c[2..3]
-    if (EPI == EPI_SWIGLU_BF16) {
-      // na is a gate row, nb the up row of the same unit: output column (n0 / 16) * 8 + gg
-      if (na < N) {
-        const float bg = bias ? bias[na] : 0.f, bu = bias ? bias[nb] : 0.f;
-        const int col = (n0 >> 1) + gg;
-        bf16* y = reinterpret_cast<bf16*>(Y);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          if (m0 + j < M) {
-            const float gate = c[j] + bg, up = c[2 + j] + bu;
-            y[(size_t)(m0 + j) * ldy + col] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
-          }
-        }
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = (j < 2) ? na : nb, m = m0 + (j & 1);
-        if (n < N && m < M) {
-          const float v = c[j] + (bias ? bias[n] : 0.f);
-          if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(Y)[(size_t)m * ldy + n] = v;
-          else reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + n] = __float2bfloat16_rn(v);
-        }
-      }
-    }
   }
+  if (S == 1) {
+    if (finisher) epilogue<EPI>(c, i, ln, n0, bias, Y, M, N, ldy);
+    return;
+  }
+  // several slices: park this CTA's tile; the CTA that arrives last adds the tiles in slice order
+  float* tile = partials + ((size_t)blockIdx.x * S) * (NT * 128);
+  if (finisher)
+    *reinterpret_cast<float4*>(tile + (size_t)slice * (NT * 128) + threadIdx.x * 4) = make_float4(c[0], c[1], c[2], c[3]);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int seen = atomicAdd(arrivals + blockIdx.x, 1);
+    is_last = (seen == S - 1);
+    if (is_last) arrivals[blockIdx.x] = 0;     // left at zero for the next launch
+  }
+  __syncthreads();
+  if (!is_last || !finisher) return;
+  __threadfence();
+  c[0] = c[1] = c[2] = c[3] = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(tile + (size_t)s * (NT * 128) + threadIdx.x * 4));
+    c[0] += v.x; c[1] += v.y; c[2] += v.z; c[3] += v.w;
+  }
+  epilogue<EPI>(c, i, ln, n0, bias, Y, M, N, ldy);
 }
 
 template <int EPI>
-static int launch(const void* X, const void* W, const float* bias, void* Y, int M, int N, int K, int ldy,
-                  cudaStream_t stream) {
-  const unsigned blocks = (unsigned)((N + 15) / 16);
-  const int threads = GEMV_WARPS * 32;
-#define AB_GO(NT) ab_launch(gemv_bf16_kernel<NT, EPI>, blocks, threads, 0, stream, (const bf16*)X, (const bf16*)W, bias, Y, M, N, K, ldy)
+static int launch(const void* X, const void* W, const float* bias, void* Y, float* partials, int* arrivals, int M,
+                  int N, int K, int ldy, int slices, cudaStream_t stream) {
+  const int n_groups = (K + 31) / 32;
+  const int gps = (n_groups + slices - 1) / slices;
+  const dim3 grid((unsigned)((N + 15) / 16), (unsigned)((n_groups + gps - 1) / gps));
+  const dim3 block(GEMV_WARPS * 32);
+#define AB_GO(NT)                                                                                                  \
+  ab_launch(gemv_bf16_kernel<NT, EPI>, grid, block, 0, stream, (const bf16*)X, (const bf16*)W, bias, Y, partials,  \
+            arrivals, M, N, K, ldy, gps)
   if (M <= 8) AB_GO(1);
   else if (M <= 16) AB_GO(2);
   else AB_GO(4);
@@ -167,16 +225,31 @@ static int launch(const void* X, const void* W, const float* bias, void* Y, int 
   return ab_launch_status();
 }
 
-// epilogue: 0 bfloat16 store, 1 float32 store, 2 SwiGLU (N = 2F interleaved rows, Y is [M, F])
-AB_API int ab_gemv_bf16(const void* X, const void* W, const float* bias, void* Y, int M, int N, int K, int ldy,
-                        int epilogue, cudaStream_t stream) {
+// How many slices of K the host should ask for, given the matrix: enough CTAs to give every
+// processor about three, but slices of at least 2048 k (with shorter slices the merge of the
+// slices costs more than the added parallelism gains: measured on 2048 x 2048).
+AB_API int ab_gemv_bf16_slices(int N, int K, int n_sms) {
+  const int slabs = (N + 15) / 16;
+  int s = (3 * n_sms + slabs - 1) / slabs;
+  const int max_s = K / 2048 > 0 ? K / 2048 : 1;
+  if (s > max_s) s = max_s;
+  if (s < 1) s = 1;
+  return s;
+}
+
+// epilogue_kind: 0 bfloat16 store, 1 float32 store, 2 SwiGLU (N = 2F interleaved rows, Y is [M, F]).
+// slices > 1 needs scratch: partials float [ceil(N/16) * slices * 128 * (1, 2 or 4 for M <= 8, 16, 32)],
+// arrivals int [ceil(N/16)], zero before the first launch and left zero by every launch.
+AB_API int ab_gemv_bf16(const void* X, const void* W, const float* bias, void* Y, float* partials, int* arrivals,
+                        int M, int N, int K, int ldy, int epilogue_kind, int slices, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return AB_OK;
-  if (M > 32 || K <= 0 || (K % 8)) return AB_BAD_ARG;
-  if (epilogue == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
-  switch (epilogue) {
-    case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(X, W, bias, Y, M, N, K, ldy, stream);
-    case EPI_STORE_F32: return launch<EPI_STORE_F32>(X, W, bias, Y, M, N, K, ldy, stream);
-    case EPI_SWIGLU_BF16: return launch<EPI_SWIGLU_BF16>(X, W, bias, Y, M, N, K, ldy, stream);
+  if (M > 32 || K <= 0 || (K % 8) || slices < 1 || slices > 65535) return AB_BAD_ARG;
+  if (slices > 1 && (!partials || !arrivals)) return AB_BAD_ARG;
+  if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  switch (epilogue_kind) {
+    case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, stream);
+    case EPI_STORE_F32: return launch<EPI_STORE_F32>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, stream);
+    case EPI_SWIGLU_BF16: return launch<EPI_SWIGLU_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, stream);
   }
   return AB_BAD_ARG;
 }

@@ -29,8 +29,8 @@
 // ---------------------------------------------------------------------------
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, const int* __restrict__ recent, int window,
                                       int vocab, float penalty) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const int* r = recent + (size_t)row * window;
   float* l = logits + (size_t)row * vocab;
@@ -141,8 +141,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
               float top_p, unsigned int seed_lo, unsigned int seed_hi, const unsigned int* __restrict__ seed_dev,
               const int* __restrict__ streams, const int* __restrict__ steps) {
   __shared__ SampleShared sh;
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const float* l = logits + (size_t)row * vocab;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

@@ -211,6 +211,14 @@ def gemm_f32(a, w, out, bias=None, n_rows=None):
 
 
 GEMV_MAX_ROWS = 16          # more rows go to the library matrix product
+_SM_COUNT: dict = {}
+
+
+def _sm_count(device) -> int:
+    n = _SM_COUNT.get(device)
+    if n is None:
+        n = _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
 
 
 def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False):
@@ -236,8 +244,16 @@ def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False):
         epi = 1 if out.dtype == torch.float32 else 0
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemv_bf16: bias f32 [N]")
-    _check(_lib("gemv_bf16").ab_gemv_bf16(_p(x), _p(w), _p(bias), _p(out), n, N, K, out.shape[-1], epi, _stream()),
-           "gemv_bf16")
+    lib = _lib("gemv_bf16")
+    slices = lib.ab_gemv_bf16_slices(N, K, _sm_count(x.device))
+    partials = arrivals = None
+    if slices > 1:
+        slabs = -(-N // 16)
+        partials = torch.empty(slabs * slices * 128 * (1 if n <= 8 else 2 if n <= 16 else 4), dtype=torch.float32,
+                               device=x.device)
+        arrivals = _arrival_counters(x.device, slabs)
+    _check(lib.ab_gemv_bf16(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K, out.shape[-1],
+                            epi, slices, _stream()), "gemv_bf16")
     return out
 
 
@@ -292,8 +308,9 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
           and k_pages.is_contiguous() and v_pages.is_contiguous(), "attention_mma: cache pages [n_pages,K,64,D]")
     lib = _lib("attention_mma")
     if ctx.is_decode:
-        chunk = lib.ab_attention_decode_chunk(D)
-        n_chunks = max(1, -(-min(ctx.max_kv_len, table.shape[1] * 64) // chunk))
+        # a CTA takes two rounds of pages per warp; the chunks must cover the whole block table
+        pages_per_cta = 2 * lib.ab_attention_decode_warps(D)
+        n_chunks = max(1, -(-table.shape[1] // pages_per_cta))
         if n_chunks > 1:
             part_o = torch.empty((T * H * n_chunks, D), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((T * H * n_chunks, 2), dtype=torch.float32, device=qkv.device)
@@ -306,7 +323,7 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
             _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(arrivals), _p(k_pages), _p(v_pages),
             _p(table),
             table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0),
-            n_chunks, _stream()), "attention_decode")
+            pages_per_cta, n_chunks, _stream()), "attention_decode")
         return out
     tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // K, qkv.device)
     _i32(ctx.tok_pos, T, "tok_pos")

@@ -44,3 +44,37 @@ def check_logits(got, want, dtype: str, what: str = "") -> None:
     assert diff.max() <= LOGIT_TOL[dtype], (f"{what}: max |diff| {diff.max():.3e} at {worst} "
                                             f"(allowed {LOGIT_TOL[dtype]:.1e}, mean {diff.mean():.3e})")
     assert diff.mean() <= LOGIT_MEAN_TOL[dtype], f"{what}: mean |diff| {diff.mean():.3e}"
+
+
+def load_part(part, seed=0, dtype="float32", std=0.3):
+    """Gives a part random weights; returns them as float64 arrays by name."""
+    import torch
+    from alpacca_b200.weights import Fetcher, RandomSource
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    src = RandomSource(part.param_specs(), seed, dt, std=std)
+    part.load(Fetcher(src, "cuda", dt))
+    return {n: src.get(n).double().numpy() for n in src.table()}
+
+
+class PartHarness:
+    """A cache and step contexts for running one mixer (or block) alone."""
+
+    def __init__(self, cache_specs, dtype="float32", max_tokens=64 * 16, max_slots=4, max_positions=1024):
+        import torch
+        from alpacca_b200.cache import SequenceCache
+        from alpacca_b200.engine.step import ContextBuilder
+        dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+        self.cache = SequenceCache(cache_specs, max_tokens, max_slots, max_positions, dt, torch.device("cuda"))
+        self.builder = ContextBuilder("cuda")
+
+    def step(self, seqs):
+        """seqs: list of (slot, number of new tokens).  Returns the context; call `done` afterwards."""
+        from alpacca_b200.engine.step import StepEntry
+        entries = [StepEntry(s, [0] * n, []) for s, n in seqs]
+        self.cache.reserve([(s, n) for s, n in seqs])
+        ctx = self.builder.build(entries, [self.cache.length(s) for s, _ in seqs], self.cache)
+        self._pending = [(s, n) for s, n in seqs]
+        return ctx
+
+    def done(self):
+        self.cache.commit(self._pending)
