@@ -530,3 +530,74 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
 #undef AB_GO
   return ab_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and described in attention_mma.h).
+// ---------------------------------------------------------------------------
+#include "attention_mma.h"
+#include <stdio.h>
+
+// partial outputs | running (max, sum) pairs | arrival counters
+static __device__ __align__(256) unsigned char ab_decode_noalloc_scratch[AB_DECODE_NOALLOC_SCRATCH_BYTES];
+
+#define AB_MAX_DEVICES 64
+static unsigned char* ab_noalloc_base[AB_MAX_DEVICES];     // device address of the array, per device
+static thread_local char ab_noalloc_message[256];
+
+AB_API const char* ab_attention_decode_bf16_noalloc_error(void) { return ab_noalloc_message; }
+
+AB_API int ab_attention_decode_bf16_noalloc(const void* qkv, int q_stride, void* out, const void* k_pages,
+                                            const void* v_pages, const int* block_table, int table_width,
+                                            const int* tok_seq, const int* kv_len, int n_tokens, int H, int K,
+                                            int D, float scale, int window, int pages_per_cta, int n_chunks,
+                                            cudaStream_t stream) {
+  ab_noalloc_message[0] = 0;
+  if (n_tokens <= 0) return AB_OK;
+  if (H <= 0 || K <= 0 || H % K || D <= 0 || n_chunks < 1) {
+    snprintf(ab_noalloc_message, sizeof ab_noalloc_message, "bad sizes: H=%d K=%d D=%d n_chunks=%d", H, K, D, n_chunks);
+    return AB_BAD_ARG;
+  }
+  const unsigned long long partial = (unsigned long long)n_tokens * H * n_chunks * D;
+  const unsigned long long counters = (unsigned long long)n_tokens * K * ((H / K + 15) / 16);
+  if (partial > AB_DECODE_NOALLOC_MAX_PARTIAL || counters > AB_DECODE_NOALLOC_MAX_COUNTERS) {
+    snprintf(ab_noalloc_message, sizeof ab_noalloc_message,
+             "problem too large for the built-in scratch: n_tokens*H*n_chunks*D = %llu (limit %u), "
+             "n_tokens*K*ceil(H/K/16) = %llu (limit %u); use ab_attention_decode_bf16 with scratch of your own",
+             partial, AB_DECODE_NOALLOC_MAX_PARTIAL, counters, AB_DECODE_NOALLOC_MAX_COUNTERS);
+    return AB_NOALLOC_TOO_LARGE;
+  }
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= AB_MAX_DEVICES) {
+    snprintf(ab_noalloc_message, sizeof ab_noalloc_message, "no usable current device (%s)", cudaGetErrorString(e));
+    return AB_CUDA_ERR + (int)e;
+  }
+  if (ab_noalloc_base[device] == nullptr) {
+    // set-up, once per device, with that device current: the array's name is a host-side handle;
+    // the address that a kernel can use has to be asked for
+    unsigned char* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, ab_decode_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(ab_noalloc_message, sizeof ab_noalloc_message, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return AB_CUDA_ERR + (int)e;
+    }
+    ab_noalloc_base[device] = p;
+  }
+  unsigned char* base = ab_noalloc_base[device];
+  float* part_o = reinterpret_cast<float*>(base);
+  float* part_ml = reinterpret_cast<float*>(base + (size_t)AB_DECODE_NOALLOC_MAX_PARTIAL * 4u);
+  int* arrivals = reinterpret_cast<int*>(base + (size_t)AB_DECODE_NOALLOC_MAX_PARTIAL * 4u +
+                                         (size_t)(AB_DECODE_NOALLOC_MAX_PARTIAL / 8u) * 4u);
+  // the counters must start at zero whatever the last call left (it may have been cut short)
+  e = cudaMemsetAsync(arrivals, 0, (size_t)counters * sizeof(int), stream);
+  if (e != cudaSuccess) {
+    snprintf(ab_noalloc_message, sizeof ab_noalloc_message, "clearing the counters failed: %s", cudaGetErrorString(e));
+    return AB_CUDA_ERR + (int)e;
+  }
+  const int rc = ab_attention_decode_bf16(qkv, q_stride, out, part_o, part_ml, arrivals, k_pages, v_pages, block_table,
+                                          table_width, tok_seq, kv_len, n_tokens, H, K, D, scale, window,
+                                          pages_per_cta, n_chunks, stream);
+  if (rc != AB_OK)
+    snprintf(ab_noalloc_message, sizeof ab_noalloc_message, "the launch was refused or failed (code %d)", rc);
+  return rc;
+}
