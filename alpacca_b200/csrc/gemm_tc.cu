@@ -1,0 +1,459 @@
+// Matrix product on the fifth-generation tensor cores: D[128 x BN] tiles of
+//   A[rowsA, K] . B[rowsB, K]^T      (both bfloat16, K contiguous)
+// accumulated in float32 in tensor memory (TMEM) by tcgen05.mma, operands staged in
+// shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), a ring of stages
+// guarded by mbarriers.
+//
+// One CTA computes one tile (and, with several K slices, one slice of it).  Six warps:
+//   warp 0      one lane issues the TMA loads of the stages,
+//   warp 1      allocates TMEM; one lane issues the MMAs (four per stage: K = 16 each)
+//               and commits them to the barriers that free the stages,
+//   warps 2..5  the epilogue: tcgen05.ld of the accumulator (a warp reads the 32 TMEM
+//               lanes it may touch), then the fused tail and the store.
+// Two uses share the kernel:
+//   rows = tokens   (prefill and large batches)  A = activations, B = weights;
+//                   tails: store bfloat16 / float32 (+ bias), or SwiGLU on the
+//                   interleaved gate|up matrix (alpacca/model.py:513);
+//   rows = features (decode, "swapped")          A = weights, B = the batch (up to 64
+//                   rows, one MMA column each): the 128-row MMA shape is filled by
+//                   the weights, which stream through once; same tails, transposed.
+// The weights never depend on the kernel before, so their first loads are issued
+// before the wait of programmatic dependent launch.
+//
+// K slices (grid z): every CTA parks its float32 tile in scratch memory; the CTA
+// that arrives last for a tile adds the slices in slice order and runs the tail.
+//
+// Every wait on an mbarrier is bounded: after SPIN_LIMIT failed tries a thread
+// records a code in `status`, and every role falls through to the common end, where
+// TMEM is given back.  The kernel cannot hang on a barrier that never completes.
+#include "common.cuh"
+#include "launch.cuh"
+#include <cuda.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define SPIN_LIMIT (1u << 22)
+
+#define EPI_STORE_BF16 0
+#define EPI_STORE_F32 1
+#define EPI_SWIGLU_BF16 2
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait; false when the limit ran out (the caller records it and leaves).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_addr(bar);
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+// K-major operand tile with 128-byte rows and 128-byte swizzle: 8-row groups are 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN> struct TcShape {
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : 4);
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+// The tail for 16 consecutive accumulator columns c0..c0+15 of row `row` of the tile.
+//   !SWAP: row = token (global row m), columns = features n0 + c
+//    SWAP: row = feature (global n), columns = batch rows c
+template <int EPI, bool SWAP>
+__device__ __forceinline__ void tail16(const float* v, int row_g, int col0_g, int rows_total, int cols_total,
+                                       const float* __restrict__ bias, void* __restrict__ Y, int ldy, int lane) {
+  if (!SWAP) {
+    const int m = row_g;
+    if (m >= rows_total) return;
+    if (EPI == EPI_SWIGLU_BF16) {
+      // columns col0..col0+7 gate, +8..+15 up of units (col0/16)*8 + 0..7
+      if (col0_g + 16 > cols_total) return;
+      bf16* y = reinterpret_cast<bf16*>(Y) + (size_t)m * ldy + (col0_g >> 1);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int u = 2 * j + e;
+          const float g = v[u] + (bias ? bias[col0_g + u] : 0.f), up = v[8 + u] + (bias ? bias[col0_g + 8 + u] : 0.f);
+          a[e] = g / (1.0f + expf(-g)) * up;
+        }
+        __nv_bfloat162 r = __floats2bfloat162_rn(a[0], a[1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&r);
+      }
+      *reinterpret_cast<uint4*>(y) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else if (EPI == EPI_STORE_F32) {
+      float* y = reinterpret_cast<float*>(Y) + (size_t)m * ldy + col0_g;
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        if (col0_g + c < cols_total) y[c] = v[c] + (bias ? bias[col0_g + c] : 0.f);
+    } else {
+      bf16* y = reinterpret_cast<bf16*>(Y) + (size_t)m * ldy + col0_g;
+      if (col0_g + 16 <= cols_total && ((ldy & 7) == 0)) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          __nv_bfloat162 r = __floats2bfloat162_rn(v[2 * j] + (bias ? bias[col0_g + 2 * j] : 0.f),
+                                                   v[2 * j + 1] + (bias ? bias[col0_g + 2 * j + 1] : 0.f));
+          w[j] = *reinterpret_cast<uint32_t*>(&r);
+        }
+        *reinterpret_cast<uint4*>(y) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(y + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c)
+          if (col0_g + c < cols_total) y[c] = __float2bfloat16_rn(v[c] + (bias ? bias[col0_g + c] : 0.f));
+      }
+    }
+  } else {
+    // swapped: this thread's row is feature n; column c is batch row m = col0_g + c
+    const int n = row_g;
+    const float b = (bias && n < rows_total) ? bias[n] : 0.f;
+    if (EPI == EPI_SWIGLU_BF16) {
+      // rows 16q..16q+7 gate, 16q+8..16q+15 up: lanes with bit 3 clear hold gates, their partner is lane + 8
+      const int unit = (n >> 4) * 8 + (n & 7);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const float mine = v[c] + b;
+        const float partner = __shfl_down_sync(0xffffffffu, mine, 8);
+        const int m = col0_g + c;
+        if (!(lane & 8) && n < rows_total && m < cols_total)
+          reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + unit] = __float2bfloat16_rn(mine / (1.0f + expf(-mine)) * partner);
+      }
+    } else {
+      if (n >= rows_total) return;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const int m = col0_g + c;
+        if (m < cols_total) {
+          if (EPI == EPI_STORE_F32) reinterpret_cast<float*>(Y)[(size_t)m * ldy + n] = v[c] + b;
+          else reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + n] = __float2bfloat16_rn(v[c] + b);
+        }
+      }
+    }
+  }
+}
+
+template <int BN, int EPI, bool SWAP>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               void* __restrict__ Y, const float* __restrict__ bias, float* __restrict__ partials,
+               int* __restrict__ arrivals, int* __restrict__ status, int rows_a, int rows_b, int K, int ldy,
+               int kblocks_per_slice) {
+  using S = TcShape<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + S::STAGES * S::STAGE_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* accum = empty + S::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  int* last_flag = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int a_row0 = blockIdx.x * TC_BM, b_row0 = blockIdx.y * BN;
+  const int n_kblocks = (K + TC_BK - 1) / TC_BK;
+  const int kb0 = blockIdx.z * kblocks_per_slice;
+  const int kb1 = min(n_kblocks, kb0 + kblocks_per_slice);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    mbar_init(accum, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(S::TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  // which operand holds the weights (independent of the kernel before this one)
+  const CUtensorMap* map_w = SWAP ? &map_a : &map_b;
+  const CUtensorMap* map_x = SWAP ? &map_b : &map_a;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      auto dst_a = [&](int s) { return base + s * S::STAGE_BYTES; };
+      auto dst_b = [&](int s) { return base + s * S::STAGE_BYTES + S::A_BYTES; };
+      auto load_w = [&](int s, int kb) {
+        if (SWAP) tma_load_2d(dst_a(s), map_w, kb * TC_BK, a_row0, full + s);
+        else tma_load_2d(dst_b(s), map_w, kb * TC_BK, b_row0, full + s);
+      };
+      auto load_x = [&](int s, int kb) {
+        if (SWAP) tma_load_2d(dst_b(s), map_x, kb * TC_BK, b_row0, full + s);
+        else tma_load_2d(dst_a(s), map_x, kb * TC_BK, a_row0, full + s);
+      };
+      const int early = min(nkb, S::STAGES);
+      for (int i = 0; i < early; ++i) {          // weights of the first stages, before the wait
+        mbar_expect_tx(full + i, S::A_BYTES + S::B_BYTES);
+        load_w(i, kb0 + i);
+      }
+      pdl_wait();
+      pdl_trigger();
+      for (int i = 0; i < early; ++i) load_x(i, kb0 + i);
+      for (int i = early; i < nkb; ++i) {
+        const int s = i % S::STAGES;
+        if (!mbar_wait(empty + s, ((i / S::STAGES) - 1) & 1)) { atomicExch(status, 1); *abort_flag = 1; break; }
+        mbar_expect_tx(full + s, S::A_BYTES + S::B_BYTES);
+        load_w(s, kb0 + i);
+        load_x(s, kb0 + i);
+      }
+    } else {
+      pdl_wait();
+    }
+  } else if (warp == 1) {
+    pdl_wait();
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((BN < 16 ? 16 : BN) >> 3) << 17) |
+                                 ((uint32_t)(TC_BM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % S::STAGES;
+        if (!mbar_wait(full + s, (i / S::STAGES) & 1)) { atomicExch(status, 2); *abort_flag = 1; ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = smem_addr(base + s * S::STAGE_BYTES), sb = sa + S::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k)
+          umma_bf16(tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(empty + s);           // frees the stage when these MMAs have read it
+      }
+      umma_commit(accum);                 // the accumulator is complete when everything before is done
+    }
+  } else {
+    pdl_wait();
+    // epilogue warps 2..5: TMEM lanes 32 * (warp % 4) .. + 31
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;          // row of the tile
+    bool ok = nkb > 0 ? mbar_wait(accum, 0) : true;
+    if (!ok) { atomicExch(status, 3); *abort_flag = 1; }
+    ok = __all_sync(0xffffffffu, ok);      // tcgen05.ld below is warp-wide
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool split = gridDim.z > 1;
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    float* my_part = partials ? partials + ((size_t)tile_id * gridDim.z + blockIdx.z) * (TC_BM * BN) : nullptr;
+    const int rows_total = SWAP ? rows_a : rows_a;        // rows of D are rows of A in both uses
+    const int cols_total = rows_b;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (nkb > 0) tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+        else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) v[c] = 0.f;
+        }
+        if (!split) {
+          tail16<EPI, SWAP>(v, a_row0 + row, b_row0 + c0, rows_total, cols_total, bias, Y, ldy, lane);
+        } else {
+          // tile stored column-chunk major so that a warp's stores are contiguous: [c0/16][row][16]
+          float4* p = reinterpret_cast<float4*>(my_part + ((size_t)(c0 >> 4) * TC_BM + row) * 16);
+          p[0] = make_float4(v[0], v[1], v[2], v[3]);
+          p[1] = make_float4(v[4], v[5], v[6], v[7]);
+          p[2] = make_float4(v[8], v[9], v[10], v[11]);
+          p[3] = make_float4(v[12], v[13], v[14], v[15]);
+        }
+      }
+    }
+    if (split) {
+      // the last CTA to arrive for this tile adds the slices in slice order (see gemv_bf16.cu)
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        const int seen = atomicAdd(arrivals + tile_id, 1);
+        const int last = (seen == (int)gridDim.z - 1);
+        if (last) arrivals[tile_id] = 0;
+        *last_flag = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag && ok) {
+        __threadfence();
+        const float* tile = partials + (size_t)tile_id * gridDim.z * (TC_BM * BN);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) v[c] = 0.f;
+          for (int s = 0; s < (int)gridDim.z; ++s) {
+            const float4* p = reinterpret_cast<const float4*>(tile + (size_t)s * (TC_BM * BN) +
+                                                               ((size_t)(c0 >> 4) * TC_BM + row) * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 t = __ldcg(p + q);
+              v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
+            }
+          }
+          tail16<EPI, SWAP>(v, a_row0 + row, b_row0 + c0, rows_total, cols_total, bias, Y, ldy, lane);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(S::TMEM_COLS));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [rows, K] bfloat16, K contiguous, boxes of 64 k x box_rows rows, 128-byte swizzle, zeros outside
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int* status_word() {
+  static int* p[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!p[dev]) {
+    if (cudaMalloc(&p[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p[dev], 0, sizeof(int));
+  }
+  return p[dev];
+}
+
+// 0 if no kernel of this library gave up on a barrier since the last call; else the code it left.
+// Synchronises the device.
+AB_API int ab_gemm_tc_status() {
+  int* p = status_word();
+  if (!p) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v) cudaMemset(p, 0, sizeof(int));
+  return v;
+}
+
+template <int BN, int EPI, bool SWAP>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, void* Y, const float* bias, float* partials,
+                     int* arrivals, int* status, int rows_a, int rows_b, int K, int ldy, int slices,
+                     cudaStream_t stream) {
+  using S = TcShape<BN>;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
+  if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;
+  const int n_kblocks = (K + TC_BK - 1) / TC_BK;
+  const int per = (n_kblocks + slices - 1) / slices;
+  dim3 grid((rows_a + TC_BM - 1) / TC_BM, (rows_b + BN - 1) / BN, (n_kblocks + per - 1) / per);
+  e = ab_launch(gemm_tc_kernel<BN, EPI, SWAP>, grid, dim3(TC_THREADS), (size_t)S::SMEM, stream, ma, mb, Y, bias,
+                partials, arrivals, status, rows_a, rows_b, K, ldy, per);
+  if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;
+  return ab_launch_status();
+}
+
+template <int EPI, bool SWAP>
+static int pick_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* Y, const float* bias, float* partials,
+                   int* arrivals, int* status, int rows_a, int rows_b, int K, int ldy, int slices, cudaStream_t stream) {
+  switch (bn) {
+    case 16: return launch_tc<16, EPI, SWAP>(ma, mb, Y, bias, partials, arrivals, status, rows_a, rows_b, K, ldy, slices, stream);
+    case 32: return launch_tc<32, EPI, SWAP>(ma, mb, Y, bias, partials, arrivals, status, rows_a, rows_b, K, ldy, slices, stream);
+    case 64: return launch_tc<64, EPI, SWAP>(ma, mb, Y, bias, partials, arrivals, status, rows_a, rows_b, K, ldy, slices, stream);
+    case 128: return launch_tc<128, EPI, SWAP>(ma, mb, Y, bias, partials, arrivals, status, rows_a, rows_b, K, ldy, slices, stream);
+    case 256: return launch_tc<256, EPI, SWAP>(ma, mb, Y, bias, partials, arrivals, status, rows_a, rows_b, K, ldy, slices, stream);
+  }
+  return AB_BAD_ARG;
+}
+
+// Y = X[M,K] . W[N,K]^T with an epilogue (0 bfloat16, 1 float32, 2 SwiGLU: W = interleaved gate|up,
+// Y [M, N/2]).  swap = 1: the weights fill the 128-row MMA operand and the batch (M <= 256) the
+// columns; bn = MMA columns per tile (16..256, a power of two).  slices > 1 needs scratch: partials
+// float [tiles * slices * 128 * bn], arrivals int [tiles] (zero before, left zero).
+AB_API int ab_gemm_tc(const void* X, const void* W, const float* bias, void* Y, float* partials, int* arrivals,
+                      int M, int N, int K, int ldy, int epilogue_kind, int swap, int bn, int slices,
+                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return AB_OK;
+  if (K <= 0 || (K % 8) || slices < 1) return AB_BAD_ARG;
+  if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  if (slices > 1 && (!partials || !arrivals)) return AB_BAD_ARG;
+  int* status = status_word();
+  if (!status) return AB_BAD_ARG;
+  CUtensorMap ma, mb;
+  const int rows_a = swap ? N : M, rows_b = swap ? M : N;
+  if (!make_map(&ma, swap ? W : X, rows_a, K, TC_BM)) return AB_BAD_ARG;
+  if (!make_map(&mb, swap ? X : W, rows_b, K, bn)) return AB_BAD_ARG;
+#define AB_GO(E)                                                                                                   \
+  return swap ? pick_bn<E, true>(bn, ma, mb, Y, bias, partials, arrivals, status, rows_a, rows_b, K, ldy, slices, stream) \
+              : pick_bn<E, false>(bn, ma, mb, Y, bias, partials, arrivals, status, rows_a, rows_b, K, ldy, slices, stream)
+  switch (epilogue_kind) {
+    case EPI_STORE_BF16: AB_GO(EPI_STORE_BF16);
+    case EPI_STORE_F32: AB_GO(EPI_STORE_F32);
+    case EPI_SWIGLU_BF16: AB_GO(EPI_SWIGLU_BF16);
+  }
+#undef AB_GO
+  return AB_BAD_ARG;
+}
