@@ -457,8 +457,13 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
 // ---------------------------------------------------------------------------
 static int dmax_of(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : 256); }
 
-// warps of a decode CTA for head size D: a CTA takes a multiple of this many pages
-AB_API int ab_attention_decode_warps(int D) { return dmax_of(D) == 64 ? 8 : (dmax_of(D) == 128 ? 4 : 2); }
+// warps of a decode CTA for head size D (a CTA takes a multiple of this many pages); `small` asks
+// for the smaller CTA, of which several fit an SM
+AB_API int ab_attention_decode_warps(int D, int small) {
+  const int dm = dmax_of(D);
+  if (small) return dm == 64 ? 4 : 2;
+  return dm == 64 ? 8 : (dm == 128 ? 4 : 2);
+}
 
 AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
                                      const void* v_pages, const int* block_table, int table_width,
@@ -498,7 +503,7 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
                                     int* arrivals, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
                                     int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
-                                    cudaStream_t stream) {
+                                    int small, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535 || pages_per_cta < 1)
     return AB_BAD_ARG;
@@ -523,8 +528,8 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
   }
   if (n_chunks > 1 && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
   switch (dmax_of(D)) {
-    case 64: AB_GO(64, 8); break;
-    case 128: AB_GO(128, 4); break;
+    case 64: if (small) AB_GO(64, 4) else AB_GO(64, 8) break;
+    case 128: if (small) AB_GO(128, 2) else AB_GO(128, 4) break;
     default: AB_GO(256, 2); break;
   }
 #undef AB_GO
@@ -596,7 +601,7 @@ AB_API int ab_attention_decode_bf16_noalloc(const void* qkv, int q_stride, void*
   }
   const int rc = ab_attention_decode_bf16(qkv, q_stride, out, part_o, part_ml, arrivals, k_pages, v_pages, block_table,
                                           table_width, tok_seq, kv_len, n_tokens, H, K, D, scale, window,
-                                          pages_per_cta, n_chunks, stream);
+                                          pages_per_cta, n_chunks, 0, stream);
   if (rc != AB_OK)
     snprintf(ab_noalloc_message, sizeof ab_noalloc_message, "the launch was refused or failed (code %d)", rc);
   return rc;

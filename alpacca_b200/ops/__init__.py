@@ -210,7 +210,8 @@ def gemm_f32(a, w, out, bias=None, n_rows=None):
     return out
 
 
-GEMV_MAX_ROWS = 16          # more rows go to the library matrix product
+GEMV_MAX_ROWS = 8           # up to here the skinny-matrix kernel is the fastest (measured per shape)
+TC_SWAP_MAX_ROWS = 64       # up to here the tcgen05 kernel with the weights on the 128-row side
 _SM_COUNT: dict = {}
 
 
@@ -308,8 +309,13 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
           and k_pages.is_contiguous() and v_pages.is_contiguous(), "attention_mma: cache pages [n_pages,K,64,D]")
     lib = _lib("attention_mma")
     if ctx.is_decode:
-        # a CTA takes two rounds of pages per warp; the chunks must cover the whole block table
-        pages_per_cta = 2 * lib.ab_attention_decode_warps(D)
+        # Few sequences: CTAs of many warps (each warp one page at a time, two rounds per CTA), the
+        # shortest chain of dependent loads.  Many sequences: CTAs of 4 warps, several per SM, which
+        # keep more pages in flight per SM.  The chunks must cover the whole block table.
+        row_tiles = -(-(H // K) // 16)
+        small = 1 if T * K * row_tiles >= 2 * _sm_count(qkv.device) else 0
+        warps = lib.ab_attention_decode_warps(D, small)
+        pages_per_cta = (4 if small else 2) * warps
         n_chunks = max(1, -(-table.shape[1] // pages_per_cta))
         if n_chunks > 1:
             part_o = torch.empty((T * H * n_chunks, D), dtype=torch.float32, device=qkv.device)
@@ -323,7 +329,7 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
             _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(arrivals), _p(k_pages), _p(v_pages),
             _p(table),
             table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0),
-            pages_per_cta, n_chunks, _stream()), "attention_decode")
+            pages_per_cta, n_chunks, small, _stream()), "attention_decode")
         return out
     tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // K, qkv.device)
     _i32(ctx.tok_pos, T, "tok_pos")
@@ -358,6 +364,8 @@ def linear_bf16(x, w, out, n_rows=None, bias=None):
           "linear_bf16: x [M,K], w [N,K], out [M,N]")
     if n <= GEMV_MAX_ROWS and x.shape[1] % 8 == 0:
         return gemv_bf16(x, w, out, bias=bias, n_rows=n)
+    if n <= TC_SWAP_MAX_ROWS and out.dtype == torch.float32 and x.shape[1] % 8 == 0:
+        return gemm_tc(x, w, out, bias=bias, n_rows=n, swap=True, slices=1)      # the vocabulary head
     if out.dtype == torch.float32:
         torch.mm(x[:n], w.t(), out_dtype=torch.float32, out=out[:n])
     else:
@@ -421,3 +429,51 @@ def decode_advance(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, 
     _check(_lib("elementwise").ab_decode_advance(
         _p(tokens), _p(tok_pos), _p(kv_len), _p(rng_step), _p(tok_seq), _p(sampled), _p(recent), _p(recent_pos),
         int(window), _p(history), _p(counter), hist_len, n_rows, _stream()), "decode_advance")
+
+
+def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None, slices=None):
+    """out[:n] = x[:n] @ w^T (+ bias) on the tcgen05 tensor cores (TMA-fed, TMEM accumulators).
+
+    x [M,K], w [N,K] bfloat16; out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row
+    interleaved gate|up matrix and out is bfloat16 [M, N/2].  `swap` puts the weights on the
+    128-row side of the MMA (the batch, up to 256 rows, becomes the columns): the shape for decode
+    steps.  `bn` is the MMA's column count per tile, `slices` the number of K slices.
+    """
+    _cuda(x, w, out, bias)
+    n = x.shape[0] if n_rows is None else n_rows
+    K, N = x.shape[1], w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+          and w.dim() == 2 and w.shape[1] == K and out.is_contiguous(), "gemm_tc: x [M,K], w [N,K] bfloat16")
+    _need(K % 8 == 0, f"gemm_tc: the inner size {K} must be a multiple of 8")
+    _need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0, "gemm_tc: operands must be 16-byte aligned")
+    _need(0 < n <= x.shape[0] and n <= out.shape[0], "gemm_tc: row count")
+    if swap is None:
+        swap = n <= 64
+    if bn is None:
+        bn = (16 if n <= 16 else 32 if n <= 32 else 64 if n <= 64 else 128 if n <= 128 else 256) if swap else 256
+    _need(bn in (16, 32, 64, 128, 256), "gemm_tc: bn must be 16, 32, 64, 128 or 256")
+    if swiglu:
+        _need(N % 16 == 0 and out.dtype == torch.bfloat16 and out.shape[-1] == N // 2,
+              "gemm_tc swiglu: w [2F,K] with F a multiple of 8, out bfloat16 [M,F]")
+        epi = 2
+    else:
+        _need(out.shape[-1] == N and out.dtype in (torch.bfloat16, torch.float32), "gemm_tc: out [M,N]")
+        epi = 1 if out.dtype == torch.float32 else 0
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemm_tc: bias f32 [N]")
+    rows_a, rows_b = (N, n) if swap else (n, N)
+    tiles = -(-rows_a // 128) * -(-rows_b // bn)
+    if slices is None:
+        slices = max(1, min(-(-2 * _sm_count(x.device) // tiles), K // 1024)) if swap else 1
+    partials = arrivals = None
+    if slices > 1:
+        partials = torch.empty(tiles * slices * 128 * bn, dtype=torch.float32, device=x.device)
+        arrivals = _arrival_counters(x.device, tiles)
+    _check(_lib("gemm_tc").ab_gemm_tc(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K,
+                                      out.shape[-1], epi, 1 if swap else 0, bn, slices, _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0, or the code left by a tcgen05 kernel that gave up waiting on a barrier (synchronises)."""
+    return _lib("gemm_tc").ab_gemm_tc_status()

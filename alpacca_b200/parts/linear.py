@@ -74,6 +74,9 @@ class Linear(Part):
         """silu(gate) * up of the interleaved gate|up product, [M, out_features / 2]."""
         n = x.shape[0] if n_rows is None else n_rows
         act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
-        if x.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.in_features % 8 == 0:
-            return ops.gemv_bf16(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True)
+        if x.dtype == torch.bfloat16 and self.in_features % 8 == 0:
+            if n <= ops.GEMV_MAX_ROWS:
+                return ops.gemv_bf16(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True)
+            if n <= ops.TC_SWAP_MAX_ROWS:
+                return ops.gemm_tc(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, swap=True, slices=1)
         return ops.swiglu(self.forward(x, n_rows=n), act, n_rows=n)

@@ -44,7 +44,7 @@ def test_no_alloc_entry_point_matches_the_package_s_own():
     lib.ab_attention_decode_bf16_noalloc_error.restype = ctypes.c_char_p
     H, K, D = 8, 2, 64
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    ppc = 2 * lib.ab_attention_decode_warps(D)
+    ppc = 2 * lib.ab_attention_decode_warps(D, 0)
     for call, lengths in enumerate(([1500, 70, 2048, 1025], [900, 2047, 33, 1300])):   # several chunks each
         qkv, k, v, table, seq, lens = _setup(lengths, H, K, D, seed=call)
         B, W = table.shape
@@ -57,7 +57,7 @@ def test_no_alloc_entry_point_matches_the_package_s_own():
         arrivals = torch.zeros(B * K, dtype=torch.int32, device="cuda")
         rc = lib.ab_attention_decode_bf16(_p(qkv), qkv.shape[1], _p(want), _p(part_o), _p(part_ml), _p(arrivals),
                                           _p(k), _p(v), _p(table), W, _p(seq), _p(lens), B, H, K, D,
-                                          ctypes.c_float(D ** -0.5), 0, ppc, n_chunks, stream)
+                                          ctypes.c_float(D ** -0.5), 0, ppc, n_chunks, 0, stream)
         assert rc == 0
         # the entry point that allocates nothing: inputs and output only
         got = torch.zeros(B, H * D, dtype=torch.bfloat16, device="cuda")
