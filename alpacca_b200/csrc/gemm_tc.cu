@@ -93,7 +93,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 
 template <int BN> struct TcShape {
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : 4);
+  // few columns: the kernel streams weights and is bound by bytes in flight, so a deep ring;
+  // many columns: bound by the tensor cores, and two CTAs per SM overlap tails with main loops
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : 8);
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;

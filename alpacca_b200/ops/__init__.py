@@ -308,14 +308,20 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
     _need(page == 64 and tuple(k_pages.shape[1:]) == (K, 64, D) and k_pages.shape == v_pages.shape
           and k_pages.is_contiguous() and v_pages.is_contiguous(), "attention_mma: cache pages [n_pages,K,64,D]")
     lib = _lib("attention_mma")
+    if ctx.is_decode and T * K * -(-(H // K) // 16) >= 2 * _sm_count(qkv.device):
+        # many (sequence, head) pairs: one warp each, no merge and no scratch
+        _i32(ctx.tok_seq, T, "tok_seq")
+        _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
+        _check(lib.ab_attention_decode_wide_bf16(
+            _p(qkv), qkv.shape[-1], _p(out), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_seq),
+            _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0), _stream()), "attention_decode_wide")
+        return out
     if ctx.is_decode:
-        # Few sequences: CTAs of many warps (each warp one page at a time, two rounds per CTA), the
-        # shortest chain of dependent loads.  Many sequences: CTAs of 4 warps, several per SM, which
-        # keep more pages in flight per SM.  The chunks must cover the whole block table.
-        row_tiles = -(-(H // K) // 16)
-        small = 1 if T * K * row_tiles >= 2 * _sm_count(qkv.device) else 0
+        # few pairs: a CTA per (sequence, head, chunk of pages), each warp one page at a time, two
+        # rounds per CTA; the chunks must cover the whole block table
+        small = 0
         warps = lib.ab_attention_decode_warps(D, small)
-        pages_per_cta = (4 if small else 2) * warps
+        pages_per_cta = 2 * warps
         n_chunks = max(1, -(-table.shape[1] // pages_per_cta))
         if n_chunks > 1:
             part_o = torch.empty((T * H * n_chunks, D), dtype=torch.float32, device=qkv.device)
