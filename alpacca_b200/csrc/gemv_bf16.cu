@@ -225,16 +225,14 @@ static int launch(const void* X, const void* W, const float* bias, void* Y, floa
   return ab_launch_status();
 }
 
-// How many slices of K the host should ask for, given the matrix: enough CTAs to give every
-// processor about three, but slices of at least 2048 k (with shorter slices the merge of the
-// slices costs more than the added parallelism gains: measured on 2048 x 2048).
+// How many slices of K the host should ask for.  Measured on a B200 (2048x2048, 3072x2048,
+// 16384x2048, 2048x8192): the merge of the slices (fence, counter, second pass) costs more than the
+// added CTAs gain, even for the 128-CTA shapes, so one slice unless K is far longer than any of those.
 AB_API int ab_gemv_bf16_slices(int N, int K, int n_sms) {
   const int slabs = (N + 15) / 16;
-  int s = (3 * n_sms + slabs - 1) / slabs;
-  const int max_s = K / 2048 > 0 ? K / 2048 : 1;
-  if (s > max_s) s = max_s;
-  if (s < 1) s = 1;
-  return s;
+  if (K < 32768 || slabs >= n_sms) return 1;
+  int s = (n_sms + slabs - 1) / slabs;
+  return s > 8 ? 8 : s;
 }
 
 // epilogue_kind: 0 bfloat16 store, 1 float32 store, 2 SwiGLU (N = 2F interleaved rows, Y is [M, F]).

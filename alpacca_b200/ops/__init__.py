@@ -222,7 +222,7 @@ def _sm_count(device) -> int:
     return n
 
 
-def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False):
+def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None):
     """out[:n] = x[:n] @ w^T (+ bias) for n <= 32 rows, bfloat16 x [M,K], w [N,K].
 
     out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row interleaved gate|up
@@ -246,7 +246,8 @@ def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False):
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemv_bf16: bias f32 [N]")
     lib = _lib("gemv_bf16")
-    slices = lib.ab_gemv_bf16_slices(N, K, _sm_count(x.device))
+    if slices is None:
+        slices = lib.ab_gemv_bf16_slices(N, K, _sm_count(x.device))
     partials = arrivals = None
     if slices > 1:
         slabs = -(-N // 16)
@@ -258,13 +259,14 @@ def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False):
     return out
 
 
-def _prefill_tiles(ctx, G, device):
-    """Tiles of query tokens for the tensor-core prefill kernel: (sequence, first packed token),
-    longest key ranges first.  Planned once per step and group size."""
-    key = ("attention_tiles", G)
+def _prefill_tiles(ctx, G, device, rows=64):
+    """Tiles of query tokens for the tensor-core prefill kernels: (sequence, first packed token),
+    longest key ranges first; a tile has `rows` query rows = rows // G tokens.  Planned once per
+    step, group size and tile height."""
+    key = ("attention_tiles", G, rows)
     plan = ctx.extras.get(key)
     if plan is None:
-        tpt = max(1, 64 // G)
+        tpt = max(1, rows // G)
         tiles, start = [], 0
         for b, (q, kv) in enumerate(zip(ctx.host_q_lens, ctx.host_kv_lens)):
             for q0 in range(0, q, tpt):
@@ -278,6 +280,7 @@ def _prefill_tiles(ctx, G, device):
 
 
 _ARRIVALS: dict = {}
+USE_TCGEN05_ATTENTION = True     # prefill steps of 128 tokens or more, head size 64: the tcgen05 kernel
 
 
 def _arrival_counters(device, n: int):
@@ -337,9 +340,18 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
             table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0),
             pages_per_cta, n_chunks, small, _stream()), "attention_decode")
         return out
-    tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // K, qkv.device)
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+    if USE_TCGEN05_ATTENTION and T >= 128 and qkv.shape[0] >= T:
+        tc = _lib("attention_tc")
+        if tc.ab_attention_prefill_tc_supports(H, K, D):
+            tile_seq, tile_q0, n_tiles, _ = _prefill_tiles(ctx, H // K, qkv.device, rows=128)
+            _check(tc.ab_attention_prefill_tc(
+                _p(qkv), T, _p(out), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(table), table.shape[1],
+                _p(ctx.tok_pos), _p(ctx.cu_q), _p(tile_seq), _p(tile_q0), n_tiles, H, K, D, ctypes.c_float(scale),
+                int(window or 0), _stream()), "attention_prefill_tc")
+            return out
+    tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // K, qkv.device)
     _check(lib.ab_attention_prefill_bf16(
         _p(qkv), qkv.shape[-1], _p(out), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
         _p(ctx.cu_q), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, K, D, ctypes.c_float(scale), int(window or 0),
@@ -483,3 +495,8 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
 def gemm_tc_status() -> int:
     """0, or the code left by a tcgen05 kernel that gave up waiting on a barrier (synchronises)."""
     return _lib("gemm_tc").ab_gemm_tc_status()
+
+
+def attention_tc_status() -> int:
+    """0, or the code left by a tcgen05 attention kernel that gave up waiting on a barrier (synchronises)."""
+    return _lib("attention_tc").ab_attention_tc_status()
