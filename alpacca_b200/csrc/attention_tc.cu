@@ -239,12 +239,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!ok) return;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < AT_D; c0 += 16) {
-        float t[16];
+      for (int c0 = 0; c0 < AT_D; c0 += 32) {        // two loads in flight, then their 32 multiply-adds
+        float t[32];
         at_ld16(tmem + lane_base + 128 + (j & 1) * 64 + c0, t);
+        at_ld16(tmem + lane_base + 128 + (j & 1) * 64 + c0 + 16, t + 16);
         at_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) o[c0 + c] = o[c0 + c] * corr + t[c];
+        for (int c = 0; c < 32; ++c) o[c0 + c] = fmaf(o[c0 + c], corr, t[c]);
       }
     };
 
@@ -261,29 +262,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const bool need_mask = (key0 + AT_KEYS - 1 > pos_first) || (window > 0);
       // the maximum is taken on the raw scores (the scale is positive), and scale and shift ride in
       // the exponent's fused multiply-add: p = 2^(s * scale - m)
-      float mx = -INFINITY;
+      // four running maxima (and below four running sums) keep the dependent chains short
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < AT_KEYS; ++c) {
+        for (int c = 0; c < AT_KEYS; ++c)
           if (key0 + c > pos || key0 + c < lo) sc[c] = -INFINITY;
-          mx = fmaxf(mx, sc[c]);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < AT_KEYS; ++c) mx = fmaxf(mx, sc[c]);
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < AT_KEYS; c += 4) {
+        mx4[0] = fmaxf(mx4[0], sc[c]);
+        mx4[1] = fmaxf(mx4[1], sc[c + 1]);
+        mx4[2] = fmaxf(mx4[2], sc[c + 2]);
+        mx4[3] = fmaxf(mx4[3], sc[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_run, mx * scale_log2);
       const float sub = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = at_exp2(m_run - sub);
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[AT_KEYS / 2];
 #pragma unroll
-      for (int c = 0; c < AT_KEYS; c += 2) {
+      for (int c = 0; c < AT_KEYS; c += 4) {
         const float p0 = at_exp2(fmaf(sc[c], scale_log2, -sub)), p1 = at_exp2(fmaf(sc[c + 1], scale_log2, -sub));
-        sum += p0 + p1;
-        __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-        packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+        const float p2 = at_exp2(fmaf(sc[c + 2], scale_log2, -sub)), p3 = at_exp2(fmaf(sc[c + 3], scale_log2, -sub));
+        sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+        __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
+        packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pa);
+        packed[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&pb);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       m_run = m_new;
       l_run = l_run * corr + sum;
       // the previous tile's product uses the P buffer of two tiles ago and must be added before O is rescaled again
