@@ -11,7 +11,7 @@ from helpers import CONFIGS, check_logits, plain_logits
 pytestmark = pytest.mark.gpu
 
 DTYPES = ("float32", "bfloat16")
-NAMES = ("a", "b", "c")
+NAMES = ("a", "b", "c", "d")
 
 
 def make_engine(model_dir, dtype, max_tokens=64 * 24, max_slots=8, max_positions=None):
@@ -23,7 +23,7 @@ def make_engine(model_dir, dtype, max_tokens=64 * 24, max_slots=8, max_positions
 
 def lengths_for(name):
     top = CONFIGS[name]["max_position_embeddings"]
-    return [n for n in (1, 9, 33, 70, 64, 65, 127) if n <= top]
+    return [n for n in (1, 9, 33, 70, 64, 65, 127, 128, 200, 331) if n <= top]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -69,9 +69,11 @@ def test_unequal_batches_one_after_another(model_dirs, name, dtype):
     d = model_dirs[(name, dtype)]
     cfg = CONFIGS[name]
     # room for one batch only, so that the second and third batches must reuse pages
-    eng = make_engine(d, dtype, max_tokens=64 * 7, max_slots=4)
+    eng = make_engine(d, dtype, max_tokens=64 * 7, max_slots=4)     # 7 pages: each batch fits, two do not
     top = cfg["max_position_embeddings"]
     batches = [[(5, 3), (70, 9), (17, 1), (33, 12)], [(1, 20), (64, 2), (40, 6)], [(63, 4), (2, 2), (90, 11), (9, 0)]]
+    if top >= 512:      # long prompts too: steps of 128 tokens and more take the tcgen05 attention
+        batches.append([(150, 3), (129, 1), (60, 2)])
     seen_slots = set()
     for bi, batch in enumerate(batches):
         reqs = []

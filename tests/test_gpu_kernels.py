@@ -368,3 +368,80 @@ def test_gemv_bf16_swiglu_epilogue(M, F, K):
     out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
     ops.gemv_bf16(x, w, out, bias=bias, swiglu=True)
     close(out, g / (1 + torch.exp(-g)) * u, "bfloat16", "swiglu epilogue")
+
+
+@pytest.mark.parametrize("M,N,K,swap,bn,slices", [
+    (128, 256, 64, False, 256, 1), (300, 520, 328, False, 128, 1), (2048, 1024, 512, False, 256, 1),
+    (8, 128, 128, True, 16, 1), (13, 1003, 200, True, 16, 1), (33, 520, 264, True, 64, 1),
+    (64, 2048, 2048, True, 64, 4), (20, 264, 4096, True, 32, 3)])
+def test_gemm_tc(M, N, K, swap, bn, slices):
+    """The tcgen05 product in both orientations, with ragged edges, K slices and both output types."""
+    from alpacca_b200 import ops
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.1), rnd(N, seed=3)
+    want = x.double() @ w.double().T + bias.double()
+    for dt, tol in ((torch.float32, "float32"), (torch.bfloat16, "bfloat16")):
+        out = torch.full((M, N), 9.0, dtype=dt, device="cuda")
+        ops.gemm_tc(x, w, out, bias=bias, swap=swap, bn=bn, slices=slices)
+        close(out, want, tol, f"gemm_tc {dt}")
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M,F,K,swap,bn", [(9, 160, 64, True, 16), (64, 264, 328, True, 64), (300, 1000, 200, False, 128),
+                                           (128, 512, 256, False, 256)])
+def test_gemm_tc_swiglu_epilogue(M, F, K, swap, bn):
+    from alpacca_b200 import ops
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    gate, up = rnd(F, K, dtype=torch.bfloat16, seed=2, scale=0.3), rnd(F, K, dtype=torch.bfloat16, seed=3, scale=0.3)
+    bg, bu = rnd(F, seed=4), rnd(F, seed=5)
+    w = torch.cat([gate.view(F // 8, 8, K), up.view(F // 8, 8, K)], dim=1).reshape(2 * F, K).contiguous()
+    bias = torch.cat([bg.view(F // 8, 8), bu.view(F // 8, 8)], dim=1).reshape(2 * F).contiguous()
+    g = x.double() @ gate.double().T + bg.double()
+    u = x.double() @ up.double().T + bu.double()
+    out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tc(x, w, out, bias=bias, swiglu=True, swap=swap, bn=bn, slices=1)
+    close(out, g / (1 + torch.exp(-g)) * u, "bfloat16", "tcgen05 swiglu epilogue")
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("H,K", [(4, 4), (8, 2), (32, 8), (16, 1), (6, 6)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_prefill_tcgen05(H, K, window):
+    """The tcgen05 prefill kernel (head size 64): whole prompts, a chunk on cached tokens, several
+    sequences in one launch; against the float64 reference and against the mma.sync kernel."""
+    from alpacca_b200 import ops
+    from alpacca_b200.cache import KVLayerView
+    from types import SimpleNamespace
+    D = 64
+    lengths, q_lens = [300, 150, 513], [300, 100, 130]
+    table, kp, vp = make_paged(lengths, 20, K, D, torch.bfloat16, seed=H)
+    T = sum(q_lens)
+    qkv = rnd(T, (H + 2 * K) * D, dtype=torch.bfloat16, seed=7)
+    ks = [rnd(n, K, D, dtype=torch.bfloat16, seed=8 + b) for b, n in enumerate(lengths)]
+    vs = [rnd(n, K, D, dtype=torch.bfloat16, seed=11 + b) for b, n in enumerate(lengths)]
+    for b in range(3):
+        fill_cache(table.cpu(), kp, vp, b, ks[b], vs[b])
+    pos = torch.cat([torch.arange(n - q, n) for n, q in zip(lengths, q_lens)]).to(torch.int32)
+    seq = torch.cat([torch.full((q,), b) for b, q in enumerate(q_lens)]).to(torch.int32)
+    cu = torch.tensor([0, 300, 400, 530], dtype=torch.int32).cuda()
+
+    def run(use_tc):
+        ctx = SimpleNamespace(tok_pos=pos.cuda(), tok_seq=seq.cuda(), n_tokens=T, n_seqs=3, cu_q=cu,
+                              kv_len=torch.tensor(lengths, dtype=torch.int32).cuda(), is_decode=False,
+                              host_q_lens=q_lens, host_kv_lens=lengths, max_q_len=300, max_kv_len=513, extras={})
+        out = torch.zeros(T, H * D, dtype=torch.bfloat16, device="cuda")
+        old = ops.USE_TCGEN05_ATTENTION
+        ops.USE_TCGEN05_ATTENTION = use_tc
+        try:
+            ops.attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, window)
+        finally:
+            ops.USE_TCGEN05_ATTENTION = old
+        return out
+    got, other = run(True), run(False)
+    assert ops.attention_tc_status() == 0
+    q = qkv.double().cpu().view(T, H + 2 * K, D)[:, :H]
+    t0 = 0
+    for b, (n, ql) in enumerate(zip(lengths, q_lens)):
+        want = ref_attention(q[t0:t0 + ql], ks[b].double().cpu(), vs[b].double().cpu(), pos[t0:t0 + ql], D ** -0.5, window)
+        close(got[t0:t0 + ql].view(ql, H, D), want, "bfloat16", f"tcgen05, sequence {b}")
+        close(other[t0:t0 + ql].view(ql, H, D), want, "bfloat16", f"mma.sync, sequence {b}")
+        t0 += ql

@@ -86,6 +86,32 @@ TINY_C = {
 }
 
 
+# A fourth one with the head size of the large models (64) and long enough positions for prompts
+# of several hundred tokens: it reaches the kernels that only take that head size.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2,
+    "hidden_size": 96,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 1,
+    "head_dim": 64,
+    "intermediate_size": 136,
+    "vocab_size": 211,
+    "max_position_embeddings": 512,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_pairing": "neox",
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "tie_word_embeddings": True,
+    "attention_bias": False,
+    "mlp_bias": False,
+    "hidden_act": "silu",
+    "bos_token_id": 1,
+    "eos_token_id": 2,
+}
+
+
 def tensor_shapes(cfg: dict) -> dict[str, tuple]:
     """Names and shapes of a checkpoint of this architecture, weights [out, in]."""
     E = cfg["hidden_size"]
