@@ -9,8 +9,8 @@ tensor is a view of the mapping until it is copied to the device.
 """
 from __future__ import annotations
 
+import ctypes
 import json
-import mmap
 import struct
 import warnings
 from dataclasses import dataclass
@@ -47,65 +47,100 @@ class TensorInfo:
 
 
 class SafetensorsFile:
-    """One mapped file; `tensors` is its table, `get(name)` a CPU view."""
+    """One mapped file; `tensors` is its table, `get(name)` a CPU view.
+
+    The file is opened, mapped, parsed and checked by the native reader
+    (`csrc/safetensors_reader.cpp`); this class is its Python face."""
+
+    _lib = None
+
+    @classmethod
+    def _reader(cls):
+        if cls._lib is None:
+            from ..ops import build
+            lib = build.load("safetensors_reader")
+            lib.st_open.restype = ctypes.c_void_p
+            lib.st_open.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int]
+            lib.st_count.argtypes = [ctypes.c_void_p]
+            lib.st_entry.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                     ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_longlong), ctypes.c_int,
+                                     ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong)]
+            lib.st_metadata_count.argtypes = [ctypes.c_void_p]
+            lib.st_metadata.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                        ctypes.POINTER(ctypes.c_char_p)]
+            lib.st_data.restype = ctypes.c_void_p
+            lib.st_data.argtypes = [ctypes.c_void_p]
+            lib.st_data_len.restype = ctypes.c_longlong
+            lib.st_data_len.argtypes = [ctypes.c_void_p]
+            lib.st_close.argtypes = [ctypes.c_void_p]
+            cls._lib = lib
+        return cls._lib
 
     def __init__(self, path):
         self.path = Path(path)
-        self._f = open(self.path, "rb")
+        lib = self._reader()
+        err = ctypes.create_string_buffer(512)
+        self._handle = lib.st_open(str(self.path).encode(), err, len(err))
+        if not self._handle:
+            raise SafetensorsError(f"{self.path}: {err.value.decode(errors='replace')}")
+        self.tensors: dict[str, TensorInfo] = {}
+        name, dtype = ctypes.c_char_p(), ctypes.c_char_p()
+        shape = (ctypes.c_longlong * 16)()
+        lo, hi = ctypes.c_longlong(), ctypes.c_longlong()
         try:
-            size = self.path.stat().st_size
-            if size < 8:
-                raise SafetensorsError(f"{self.path}: too short to be a safetensors file ({size} bytes)")
-            (hlen,) = struct.unpack("<Q", self._f.read(8))
-            if hlen > size - 8:
-                raise SafetensorsError(f"{self.path}: header length {hlen} exceeds the file ({size} bytes)")
-            try:
-                header = json.loads(self._f.read(hlen).decode("utf-8"))
-            except (UnicodeDecodeError, json.JSONDecodeError) as e:
-                raise SafetensorsError(f"{self.path}: header is not JSON: {e}") from None
-            if not isinstance(header, dict):
-                raise SafetensorsError(f"{self.path}: header must be a JSON object")
-            self.data_start = 8 + hlen
-            data_len = size - self.data_start
-            self.metadata = header.pop("__metadata__", {}) or {}
-            self.tensors: dict[str, TensorInfo] = {}
-            for name, info in header.items():
-                try:
-                    dt, shape = info["dtype"], tuple(int(s) for s in info["shape"])
-                    lo, hi = (int(x) for x in info["data_offsets"])
-                except (KeyError, TypeError, ValueError):
-                    raise SafetensorsError(f"{self.path}: malformed entry for tensor {name}") from None
+            for i in range(lib.st_count(self._handle)):
+                rank = lib.st_entry(self._handle, i, ctypes.byref(name), ctypes.byref(dtype), shape, 16,
+                                    ctypes.byref(lo), ctypes.byref(hi))
+                n, dt = name.value.decode(), dtype.value.decode()
+                if rank > 16:
+                    raise SafetensorsError(f"{self.path}: tensor {n} has {rank} dimensions")
                 if dt not in DTYPES:
-                    raise SafetensorsError(f"{self.path}: tensor {name} has unsupported dtype {dt}")
-                ti = TensorInfo(name, dt, shape, lo, hi)
-                want = ti.numel * DTYPES[dt].itemsize
-                if lo < 0 or hi < lo or hi > data_len:
-                    raise SafetensorsError(f"{self.path}: tensor {name} lies outside the file "
-                                           f"(offsets {lo}..{hi}, data section {data_len} bytes)")
-                if hi - lo != want:
-                    raise SafetensorsError(f"{self.path}: tensor {name} of shape {list(shape)} {dt} "
-                                           f"needs {want} bytes, has {hi - lo}")
-                self.tensors[name] = ti
-            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size else None
+                    raise SafetensorsError(f"{self.path}: tensor {n} has unsupported dtype {dt}")
+                self.tensors[n] = TensorInfo(n, dt, tuple(shape[d] for d in range(rank)), lo.value, hi.value)
+            self.metadata = {}
+            key, value = ctypes.c_char_p(), ctypes.c_char_p()
+            for i in range(lib.st_metadata_count(self._handle)):
+                lib.st_metadata(self._handle, i, ctypes.byref(key), ctypes.byref(value))
+                self.metadata[key.value.decode()] = value.value.decode()
+            self._data = lib.st_data(self._handle)
+            self._data_len = lib.st_data_len(self._handle)
         except Exception:
-            self._f.close()
+            self.close()
             raise
 
     def get(self, name: str) -> torch.Tensor:
-        """A read-only CPU view of the tensor in its stored dtype (copy it before writing)."""
+        """A read-only CPU view of the tensor in its stored dtype (copy it before writing).  The view
+        keeps the file mapped for as long as it lives."""
+        if not self._handle:
+            raise SafetensorsError(f"{self.path} is closed")
         ti = self.tensors[name]
         if ti.numel == 0:
             return torch.empty(ti.shape, dtype=DTYPES[ti.dtype])
+        raw = (ctypes.c_ubyte * (ti.end - ti.begin)).from_address(self._data + ti.begin)
         with warnings.catch_warnings():   # the mapping is read-only; callers copy before writing
             warnings.simplefilter("ignore", UserWarning)
-            t = torch.frombuffer(self._mm, dtype=DTYPES[ti.dtype], count=ti.numel,
-                                 offset=self.data_start + ti.begin)
-        return t.reshape(ti.shape)
+            t = torch.frombuffer(raw, dtype=DTYPES[ti.dtype], count=ti.numel)
+        t = t.reshape(ti.shape)
+        t._alpacca_file = self            # a view must not outlive the mapping
+        self._views += 1
+        return t
+
+    _views = 0
 
     def close(self):
-        # views handed out keep the mapping alive; closing only drops our handles
-        self._mm = None
-        self._f.close()
+        """Unmaps the file, unless views of it were handed out: then the mapping lives as long as
+        this object (which every view refers to)."""
+        if self._handle and self._views == 0:
+            self._reader().st_close(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_handle", None):
+                self._reader().st_close(self._handle)
+                self._handle = None
+        except Exception:
+            pass
 
 
 def write_safetensors(path, entries, metadata: dict | None = None) -> None:
