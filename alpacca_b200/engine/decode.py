@@ -83,6 +83,8 @@ class _Shape:
         self.sect = {n: (self.offs[i], sizes[i]) for i, n in enumerate(names)}
         self.table_sect = [(self.offs[len(names) + g], rows * width) for g in range(n_groups)]
         self.recent_sect = (self.offs[len(names) + n_groups], rows * R)
+        o, n = self.sect["tok_seq"]
+        self.mask_host, self.mask_dev = self.host[o:o + n], self.dev[o:o + n]   # the live mask of the rows
         self.sampled = torch.zeros(rows, dtype=torch.int32, device=dev)
         self.sampled_host = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
         self.history = torch.zeros((dec.history_len, rows), dtype=torch.int32, device=dev)
@@ -128,6 +130,7 @@ class GraphDecoder:
         self.mask: list = []
         self.expect: dict = {}          # slot -> (length, last sampled token) after the last step
         self.pages_seen = -1
+        self._last_slots, self._last_rows, self._room = None, None, 0
 
     # -- the captured step -------------------------------------------------------------
     def _body(self, sh: _Shape):
@@ -216,6 +219,25 @@ class GraphDecoder:
         a sequence that ended is masked out (its row becomes padding) until so few are left that a
         smaller shape pays.  Returns the row of each live sequence."""
         cache = self.engine.cache
+        slots = [slot for slot, _, _ in live]
+        sh = self.shape
+        # the usual case, kept short: the same sequences as in the last step, each continued exactly
+        # where that step left it, with room left in the pages they hold
+        if (sh is not None and slots == self._last_slots and self._room >= steps
+                and all(self.expect.get(slot) in ((cache.length(slot), tok), (cache.length(slot), None))
+                        for slot, tok, _ in live)):
+            self._room -= steps
+            if always_mask:
+                sh.mask_dev.copy_(sh.mask_host, non_blocking=True)
+            return self._last_rows
+        rows = self._prepare_slow(live, steps, always_mask)
+        self._last_slots, self._last_rows = slots, rows
+        self._room = min([len(g.page_lists[s]) * PAGE_SIZE - cache.length(s) for g in cache.kv_groups for s in slots]
+                         + [1 << 30]) - steps
+        return rows
+
+    def _prepare_slow(self, live, steps: int, always_mask: bool):
+        cache = self.engine.cache
         self._reserve(live, steps)
         need_pages = max([len(grp.page_lists[slot]) for grp in cache.kv_groups for slot, _, _ in live] + [1])
         slots = [slot for slot, _, _ in live]
@@ -251,9 +273,8 @@ class GraphDecoder:
             if mask != self.mask:
                 torch.cuda.current_stream().synchronize()
             self.mask = mask
-            o, n = sh.sect["tok_seq"]
-            sh.host[o:o + n] = torch.tensor(mask, dtype=torch.int32)
-            sh.dev[o:o + n].copy_(sh.host[o:o + n], non_blocking=True)
+            sh.mask_host.copy_(torch.tensor(mask, dtype=torch.int32))
+            sh.mask_dev.copy_(sh.mask_host, non_blocking=True)
         return rows
 
     def _upload_tables(self, layout_entries):
@@ -310,6 +331,7 @@ class GraphDecoder:
             self.sampler = sampler
         self.shape, self.layout, self.row_of, self.mask, self.pages_seen = None, [], {}, [], -1
         self.expect = {}
+        self._last_slots, self._last_rows, self._room = None, None, 0
 
     def close(self):
         self.shapes.clear()
