@@ -11,7 +11,8 @@
 //            them.  Any mix of sequences: tokens on top of cached ones, chunks,
 //            single tokens; the host lists the tiles.
 //   decode   one new token per sequence: one CTA per (sequence, KV head, chunk
-//            of keys); each warp takes one page of the chunk, the warps'
+//            of keys); the keys are the rows of the tensor-core tiles and the group's
+//            heads the columns; each warp takes a run of 16-key tiles, the warps'
 //            results are merged in shared memory.  The chunks' partial results
 //            go to scratch memory, and the CTA that finishes last for its
 //            (sequence, KV head) merges them, always in chunk order, so the
@@ -22,6 +23,7 @@
 // (alpacca/model.py:447-467).  Head sizes: multiples of 16 up to 256.
 #include "common.cuh"
 #include "launch.cuh"
+#include <cooperative_groups.h>
 #include <cuda_pipeline.h>
 
 #define PAGE 64
@@ -286,10 +288,136 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
 }
 
 // ---------------------------------------------------------------------------
-// decode: one token per sequence; grid (sequence, KV head x row tile, chunk).
-// A chunk is `pages_per_cta` pages; warp w of the CTA takes the chunk's pages
-// w, w + NWARPS, ... one after another.
+// decode: one token per sequence; grid (sequence, KV head x tile of 8 heads of
+// its group, chunk of keys).
+//
+// With one query token the roles of the operands are swapped: the KEYS are the
+// 16 rows of the tensor-core tile and the (up to 8) query heads of the group
+// its 8 columns, S^T = K Q^T and O^T = V^T P^T, so that no row of a tile is
+// padding.  P^T as the second operand is the transposed accumulator of S^T
+// (movmatrix).  A warp takes a run of up to DECODE_RUN consecutive 16-key tiles
+// per round; the chunk's tiles are dealt to the warps in equal runs.  Rounds
+// follow one another, so the CTA has as many warps as shared memory has room
+// for runs: at head size 64, 16 warps x 48 keys = 12 pages in one round.
 // ---------------------------------------------------------------------------
+#define DECODE_RUN 3
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+
+// Running state of one warp: thread (g = lane/4, t = lane%4) holds heads 2t, 2t+1 of
+// O^T[d = 16*dm + g (+8)], and the running maximum and (per-thread part of the) sum of those heads.
+template <int DMAX>
+struct DecodeState {
+  float o[DMAX / 16][4];
+  float m[2];
+  float l[2];
+};
+
+// One run of `nt` (1..DECODE_RUN) 16-key tiles; ks, vs: the run's keys and values [nt*16][pitch];
+// qb: Q^T as the second operand, per 16 columns of the head; key0: position of the run's first key.
+template <int DMAX>
+__device__ __forceinline__ void attend_run(DecodeState<DMAX>& st, const uint32_t (&qb)[DMAX / 16][2], const bf16* ks,
+                                           const bf16* vs, int pitch, int D, float scale_log2, int nt, int key0,
+                                           int pos, int lo) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+  float s[DECODE_RUN][4];
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < DECODE_RUN; ++i) {
+    if (i < nt) {
+      s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kd = 0; kd < DMAX / 16; ++kd) {
+        if (kd * 16 < D) {
+          uint32_t a0, a1, a2, a3;
+          ldmatrix_x4(a0, a1, a2, a3, smem_u32(ks + (i * 16 + a_row) * pitch + kd * 16 + a_col));
+          mma_bf16(s[i], a0, a1, a2, a3, qb[kd][0], qb[kd][1]);
+        }
+      }
+      const int ka = key0 + i * 16 + g, kb = ka + 8;
+      const bool oka = ka <= pos && ka >= lo, okb = kb <= pos && kb >= lo;
+      s[i][0] = oka ? s[i][0] * scale_log2 : -INFINITY;
+      s[i][1] = oka ? s[i][1] * scale_log2 : -INFINITY;
+      s[i][2] = okb ? s[i][2] * scale_log2 : -INFINITY;
+      s[i][3] = okb ? s[i][3] * scale_log2 : -INFINITY;
+    } else {
+      s[i][0] = s[i][1] = s[i][2] = s[i][3] = -INFINITY;
+    }
+    mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][2]));
+    mx1 = fmaxf(mx1, fmaxf(s[i][1], s[i][3]));
+  }
+  // a head's keys are spread over the lanes' g: bits 2..4 of the lane
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+  }
+  const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+  const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
+  const float corr0 = exp2f(st.m[0] - sub0), corr1 = exp2f(st.m[1] - sub1);
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < DECODE_RUN; ++i) {
+    s[i][0] = exp2f(s[i][0] - sub0);
+    s[i][1] = exp2f(s[i][1] - sub1);
+    s[i][2] = exp2f(s[i][2] - sub0);
+    s[i][3] = exp2f(s[i][3] - sub1);
+    sum0 += s[i][0] + s[i][2];
+    sum1 += s[i][1] + s[i][3];
+  }
+  st.m[0] = mn0;
+  st.m[1] = mn1;
+  st.l[0] = st.l[0] * corr0 + sum0;
+  st.l[1] = st.l[1] * corr1 + sum1;
+#pragma unroll
+  for (int dm = 0; dm < DMAX / 16; ++dm) {
+    st.o[dm][0] *= corr0;
+    st.o[dm][1] *= corr1;
+    st.o[dm][2] *= corr0;
+    st.o[dm][3] *= corr1;
+  }
+  // O^T += V^T P^T
+  const int v_key = (lane & 7) + (lane >> 4) * 8, v_col = ((lane >> 3) & 1) * 8;
+#pragma unroll
+  for (int i = 0; i < DECODE_RUN; ++i) {
+    if (i < nt) {
+      const uint32_t b0 = movmatrix_trans(pack_bf16(s[i][0], s[i][1]));
+      const uint32_t b1 = movmatrix_trans(pack_bf16(s[i][2], s[i][3]));
+#pragma unroll
+      for (int dm = 0; dm < DMAX / 16; ++dm) {
+        if (dm * 16 < D) {
+          uint32_t a0, a1, a2, a3;
+          ldmatrix_x4_trans(a0, a1, a2, a3, smem_u32(vs + (i * 16 + v_key) * pitch + dm * 16 + v_col));
+          mma_bf16(st.o[dm], a0, a1, a2, a3, b0, b1);
+        }
+      }
+    }
+  }
+}
+
+// Asks for tiles [t0, t1) of KV head kh (16 keys each, inside one page each) into ks, vs [.][pitch].
+// `skip_key` (or -1): the row of the token that the step is writing, fetched later.
+__device__ __forceinline__ void load_run_async(bf16* ks, bf16* vs, const bf16* __restrict__ k_pages,
+                                               const bf16* __restrict__ v_pages, const int* __restrict__ bt, int K,
+                                               int kh, int D, int pitch, int t0, int t1, int skip_key, int lane) {
+  const int cpr = D >> 3;
+  for (int tl = t0; tl < t1; ++tl) {
+    const size_t base = ((size_t)bt[tl >> 2] * K + kh) * PAGE * D + (size_t)(tl & 3) * 16 * D;
+    for (int c = lane; c < 16 * cpr; c += 32) {
+      const int r = c / cpr, cc = c - r * cpr;
+      if (tl * 16 + r == skip_key) continue;
+      const int dst = ((tl - t0) * 16 + r) * pitch + cc * 8;
+      cp_async_16(ks + dst, k_pages + base + (size_t)r * D + cc * 8);
+      cp_async_16(vs + dst, v_pages + base + (size_t)r * D + cc * 8);
+    }
+  }
+}
+
 template <int DMAX, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
@@ -297,123 +425,150 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
                         const int* __restrict__ kv_len, int H, int K, int D, float scale_log2, int window,
-                        int pages_per_cta, int n_chunks) {
+                        int pages_per_cta, int n_chunks, int cluster_merge) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch = D + 8;
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][pitch]
-  bf16* kv = qs + 16 * pitch;                                   // [NWARPS][2][64][pitch]
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [8][pitch]
+  bf16* kv = qs + 8 * pitch;                                    // [NWARPS][2][16 * DECODE_RUN][pitch]
 
   // What this kernel reads before the wait was written in earlier steps (lengths, block table,
-  // every page but the one that holds this step's token), never by the kernels just before it.
+  // every cached row but the one of this step's token), never by the kernels just before it.
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
-  const int row_tiles = (G + 15) / 16;
+  const int row_tiles = (G + 7) / 8;
   const int tok = blockIdx.x;
   const int kh = blockIdx.y / row_tiles, rt = blockIdx.y - kh * row_tiles;
   const int chunk = blockIdx.z;
-  // In a decode step row `tok` of the batch is sequence `tok` (or padding: tok_seq < 0), so the
-  // sequence's length and its block-table entries are asked for together with the padding mark
-  // instead of one after the other.
+  // In a decode step row `tok` of the batch is sequence `tok` (or padding: tok_seq < 0).
   const int* bt = block_table + (size_t)tok * table_width;
   const int b = tok_seq[tok];
   const int len = kv_len[tok];
-  const int my_first = chunk * pages_per_cta + warp;
-  const int my_first_entry = my_first < table_width ? bt[my_first] : 0;
   if (b < 0) { pdl_wait(); pdl_trigger(); return; }
   const int pos = len - 1;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int first_page = lo / PAGE, last_page = pos / PAGE;
   const int first_chunk = first_page / pages_per_cta, last_chunk = last_page / pages_per_cta;
-  if (chunk < first_chunk || chunk > last_chunk) { pdl_wait(); pdl_trigger(); return; }
-  const int n_rows = min(16, G - rt * 16);
+  // a chunk without visible keys has nothing to do; as a member of a cluster it still has to meet
+  // the others at the cluster's barriers
+  const bool active = chunk >= first_chunk && chunk <= last_chunk;
+  if (!active && !cluster_merge) { pdl_wait(); pdl_trigger(); return; }
+  const int n_heads = min(8, G - rt * 8);
 
-  RowState<DMAX> st;
-  init_state(st);
-  bf16* ks = kv + (size_t)warp * 2 * 64 * pitch;
-  bf16* vs = ks + 64 * pitch;
-  const int page_begin = max(chunk * pages_per_cta, first_page);
-  const int page_end = min((chunk + 1) * pages_per_cta, last_page + 1);
-  int page = page_begin + warp;
-  // the first page of this warp, unless it is the one being written right now, is fetched before the wait
-  const bool early = page < page_end && page != last_page;
-  if (early) {
-    const size_t base = ((size_t)(page == my_first ? my_first_entry : bt[page]) * K + kh) * PAGE * D;
-    load_tile_async(ks, k_pages + base, D, pitch, lane, 32);
-    load_tile_async(vs, v_pages + base, D, pitch, lane, 32);
-    cp_async_commit();
-  }
+  // this chunk's 16-key tiles, dealt to the warps in equal runs of at most DECODE_RUN, round after round
+  const int tile_begin = max(chunk * pages_per_cta * (PAGE / 16), lo / 16);
+  const int tile_end = active ? min((chunk + 1) * pages_per_cta * (PAGE / 16), pos / 16 + 1) : tile_begin;
+  const int n_tiles = max(tile_end - tile_begin, 1);
+  const int rounds = (n_tiles + NWARPS * DECODE_RUN - 1) / (NWARPS * DECODE_RUN);
+  const int per_run = (n_tiles + NWARPS * rounds - 1) / (NWARPS * rounds);
+
+  DecodeState<DMAX> st;
+#pragma unroll
+  for (int dm = 0; dm < DMAX / 16; ++dm) st.o[dm][0] = st.o[dm][1] = st.o[dm][2] = st.o[dm][3] = 0.f;
+  st.m[0] = st.m[1] = -INFINITY;
+  st.l[0] = st.l[1] = 0.f;
+  bf16* ks = kv + (size_t)warp * 2 * 16 * DECODE_RUN * pitch;
+  bf16* vs = ks + 16 * DECODE_RUN * pitch;
+  int t0 = min(tile_end, tile_begin + warp * per_run), t1 = min(tile_end, t0 + per_run);
+  load_run_async(ks, vs, k_pages, v_pages, bt, K, kh, D, pitch, t0, t1, pos, lane);
+  cp_async_commit();
   pdl_wait();
   pdl_trigger();
+  if (pos >= t0 * 16 && pos < t1 * 16) {
+    // the row that this step wrote
+    const int tl = pos >> 4, r = pos & 15;
+    const size_t base = ((size_t)bt[tl >> 2] * K + kh) * PAGE * D + (size_t)((tl & 3) * 16 + r) * D;
+    const int dst = ((tl - t0) * 16 + r) * pitch;
+    for (int cc = lane; cc < (D >> 3); cc += 32) {
+      cp_async_16(ks + dst + cc * 8, k_pages + base + cc * 8);
+      cp_async_16(vs + dst + cc * 8, v_pages + base + cc * 8);
+    }
+    cp_async_commit();
+  }
   {
     const int cpr = D >> 3;
-    for (int c = tid; c < 16 * cpr; c += NWARPS * 32) {
+    for (int c = tid; c < 8 * cpr; c += NWARPS * 32) {
       const int r = c / cpr, cc = c - r * cpr;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < n_rows)
-        v = *reinterpret_cast<const uint4*>(qkv + (size_t)tok * q_stride + (size_t)(kh * G + rt * 16 + r) * D + cc * 8);
+      if (r < n_heads)
+        v = *reinterpret_cast<const uint4*>(qkv + (size_t)tok * q_stride + (size_t)(kh * G + rt * 8 + r) * D + cc * 8);
       *reinterpret_cast<uint4*>(qs + r * pitch + cc * 8) = v;
     }
   }
   __syncthreads();
-  for (bool first = true; page < page_end; page += NWARPS, first = false) {
-    if (!(first && early)) {
-      const size_t base = ((size_t)bt[page] * K + kh) * PAGE * D;
-      load_tile_async(ks, k_pages + base, D, pitch, lane, 32);
-      load_tile_async(vs, v_pages + base, D, pitch, lane, 32);
+  uint32_t qb[DMAX / 16][2];
+#pragma unroll
+  for (int kd = 0; kd < DMAX / 16; ++kd) {
+    if (kd * 16 < D) {
+      qb[kd][0] = *reinterpret_cast<const uint32_t*>(qs + g * pitch + kd * 16 + 2 * t4);
+      qb[kd][1] = *reinterpret_cast<const uint32_t*>(qs + g * pitch + kd * 16 + 8 + 2 * t4);
+    } else {
+      qb[kd][0] = qb[kd][1] = 0u;
+    }
+  }
+  for (int round = 0; round < rounds; ++round) {
+    if (round > 0) {
+      t0 = min(tile_end, tile_begin + (round * NWARPS + warp) * per_run);
+      t1 = min(tile_end, t0 + per_run);
+      load_run_async(ks, vs, k_pages, v_pages, bt, K, kh, D, pitch, t0, t1, -1, lane);
       cp_async_commit();
     }
     cp_async_wait<0>();
     __syncwarp();
-    const int key0 = page * PAGE;
-    const bool need_mask = (key0 + PAGE - 1 > pos) || (key0 < lo);
-    attend_tile<DMAX>(st, qs, ks, vs, pitch, D, scale_log2, key0, pos, pos, lo, lo, need_mask);
-    __syncwarp();      // every lane is done reading the tile before the next one overwrites it
+    if (t0 < t1) attend_run<DMAX>(st, qb, ks, vs, pitch, D, scale_log2, t1 - t0, t0 * 16, pos, lo);
+    __syncwarp();      // every lane is done reading the run before the next one overwrites it
   }
   float l0 = st.l[0], l1 = st.l[1];
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+  }
   __syncthreads();      // every warp is done with its tiles: shared memory is reused below
 
-  // merge the warps: sm_o [NWARPS][16][D], sm_m, sm_l [NWARPS][16]
+  // merge the warps: sm_o [NWARPS][8][D + 4], sm_m, sm_l [NWARPS][8]
+  const int op = D + 4;
   float* sm_o = reinterpret_cast<float*>(kv);
-  float* sm_m = sm_o + NWARPS * 16 * D;
-  float* sm_l = sm_m + NWARPS * 16;
+  float* sm_m = sm_o + NWARPS * 8 * op;
+  float* sm_l = sm_m + NWARPS * 8;
+  float* cta_o = sm_l + NWARPS * 8;      // [8][D]: this CTA's result, read by its cluster
+  float* cta_ml = cta_o + 8 * D;         // [8][2]
 #pragma unroll
-  for (int dt = 0; dt < DMAX / 8; ++dt) {
-    if (dt * 8 < D) {
-      const int d = dt * 8 + 2 * t4;
-      sm_o[(warp * 16 + g) * D + d] = st.o[dt][0];
-      sm_o[(warp * 16 + g) * D + d + 1] = st.o[dt][1];
-      sm_o[(warp * 16 + g + 8) * D + d] = st.o[dt][2];
-      sm_o[(warp * 16 + g + 8) * D + d + 1] = st.o[dt][3];
+  for (int dm = 0; dm < DMAX / 16; ++dm) {
+    if (dm * 16 < D) {
+      const int d = dm * 16 + g;
+      sm_o[(warp * 8 + 2 * t4) * op + d] = st.o[dm][0];
+      sm_o[(warp * 8 + 2 * t4 + 1) * op + d] = st.o[dm][1];
+      sm_o[(warp * 8 + 2 * t4) * op + d + 8] = st.o[dm][2];
+      sm_o[(warp * 8 + 2 * t4 + 1) * op + d + 8] = st.o[dm][3];
     }
   }
-  if (t4 == 0) {
-    sm_m[warp * 16 + g] = st.m[0];
-    sm_m[warp * 16 + g + 8] = st.m[1];
-    sm_l[warp * 16 + g] = l0;
-    sm_l[warp * 16 + g + 8] = l1;
+  if (g == 0) {
+    sm_m[warp * 8 + 2 * t4] = st.m[0];
+    sm_m[warp * 8 + 2 * t4 + 1] = st.m[1];
+    sm_l[warp * 8 + 2 * t4] = l0;
+    sm_l[warp * 8 + 2 * t4 + 1] = l1;
   }
   __syncthreads();
   const bool single = (first_chunk == last_chunk);
-  for (int idx = tid; idx < n_rows * D; idx += NWARPS * 32) {
+  for (int idx = tid; idx < n_heads * D; idx += NWARPS * 32) {
     const int r = idx / D, d = idx - r * D;
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < NWARPS; ++w) m = fmaxf(m, sm_m[w * 16 + r]);
+    for (int w = 0; w < NWARPS; ++w) m = fmaxf(m, sm_m[w * 8 + r]);
     float l = 0.f, o = 0.f;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) {
-      const float mw = sm_m[w * 16 + r];
+      const float mw = sm_m[w * 8 + r];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
-      l += sm_l[w * 16 + r] * f;
-      o += sm_o[(w * 16 + r) * D + d] * f;
+      l += sm_l[w * 8 + r] * f;
+      o += sm_o[(w * 8 + r) * op + d] * f;
     }
-    const int h = kh * G + rt * 16 + r;
-    if (single) {
+    const int h = kh * G + rt * 8 + r;
+    if (cluster_merge) {
+      cta_o[r * D + d] = o;
+      if (d == 0) { cta_ml[r * 2] = m; cta_ml[r * 2 + 1] = l; }
+    } else if (single) {
       out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     } else {
       const size_t p = ((size_t)tok * H + h) * n_chunks + chunk;
@@ -421,9 +576,34 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
       if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
     }
   }
+  if (cluster_merge) {
+    // The chunks of one (token, KV head, head tile) are the CTAs of one cluster: the first of them
+    // reads the others' results from their shared memory, in chunk order.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (chunk == 0) {
+      for (int idx = tid; idx < n_heads * D; idx += NWARPS * 32) {
+        const int r = idx / D, d = idx - r * D;
+        float m = -INFINITY;
+        for (int c = first_chunk; c <= last_chunk; ++c) m = fmaxf(m, cluster.map_shared_rank(cta_ml, c)[r * 2]);
+        float l = 0.f, o = 0.f;
+        for (int c = first_chunk; c <= last_chunk; ++c) {
+          const float* ml = cluster.map_shared_rank(cta_ml, c);
+          const float mc = ml[r * 2];
+          const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - m);
+          l += ml[r * 2 + 1] * f;
+          o += cluster.map_shared_rank(cta_o, c)[r * D + d] * f;
+        }
+        out[((size_t)tok * H + kh * G + rt * 8 + r) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+      }
+    }
+    cluster.sync();      // nobody leaves while the first CTA still reads its shared memory
+    return;
+  }
   if (single) return;
 
-  // The last CTA to arrive for this (token, KV head, row tile) merges the chunks.  Each CTA
+  // The last CTA to arrive for this (token, KV head, head tile) merges the chunks.  Each CTA
   // publishes its partials (fence), then counts itself; the one that sees all others has, by the
   // fence on the other side, their partials in view.  It puts the counter back to zero for the
   // next launch.
@@ -440,9 +620,9 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = tid; idx < n_rows * D; idx += NWARPS * 32) {
+  for (int idx = tid; idx < n_heads * D; idx += NWARPS * 32) {
     const int r = idx / D, d = idx - r * D;
-    const int h = kh * G + rt * 16 + r;
+    const int h = kh * G + rt * 8 + r;
     const size_t base = ((size_t)tok * H + h) * n_chunks;
     float m = -INFINITY;
     for (int c = first_chunk; c <= last_chunk; ++c) m = fmaxf(m, __ldcg(part_ml + (base + c) * 2));
@@ -562,13 +742,15 @@ attention_decode_wide_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* _
 // ---------------------------------------------------------------------------
 static int dmax_of(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : 256); }
 
-// warps of a decode CTA for head size D (a CTA takes a multiple of this many pages); `small` asks
-// for the smaller CTA, of which several fit an SM
+// warps of a decode CTA for head size D (`small` is ignored: there is one CTA size per head size)
 AB_API int ab_attention_decode_warps(int D, int small) {
+  (void)small;
   const int dm = dmax_of(D);
-  if (small) return dm == 64 ? 4 : 2;
-  return dm == 64 ? 8 : (dm == 128 ? 4 : 2);
+  return dm == 64 ? 16 : (dm == 128 ? 8 : 4);
 }
+
+// pages that a decode CTA covers in one round: its warps' runs of DECODE_RUN tiles of 16 keys
+AB_API int ab_attention_decode_round_pages(int D) { return ab_attention_decode_warps(D, 0) * DECODE_RUN * 16 / PAGE; }
 
 AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
                                      const void* v_pages, const int* block_table, int table_width,
@@ -601,9 +783,41 @@ AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, c
   return ab_launch_status();
 }
 
-// Scratch (only touched when n_chunks > 1): part_o float [n_tokens * H * n_chunks, D], part_ml float
-// [n_tokens * H * n_chunks, 2], arrivals int [n_tokens * K * ceil(G / 16)], which must be zero before
-// the first launch and is left zero by every launch.
+// Launch with programmatic dependent launch and, for `cluster_z` > 1, clusters of that many CTAs along z.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, unsigned cluster_z, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (ab_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = cluster_z;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define AB_DECODE_MAX_CLUSTER 8
+
+// The chunks of one (token, KV head) are merged inside a thread-block cluster (through shared
+// memory) when there are 2 to 8 of them.  More chunks than that go through scratch memory:
+// part_o float [n_tokens * H * n_chunks, D], part_ml float [n_tokens * H * n_chunks, 2], arrivals int
+// [n_tokens * K * ceil(G / 8)], which must be zero before the first launch and is left zero by every
+// launch.
 AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
                                     int* arrivals, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
@@ -613,31 +827,34 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
   if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535 || pages_per_cta < 1)
     return AB_BAD_ARG;
   if ((long long)pages_per_cta * n_chunks < table_width) return AB_BAD_ARG;   // the chunks must cover the table
-  const int G = H / K, row_tiles = (G + 15) / 16;
+  const int G = H / K, row_tiles = (G + 7) / 8;
   if ((long long)K * row_tiles > 65535) return AB_BAD_ARG;
   const int pitch = D + 8;
   const float sl = scale * LOG2E;
+  const int cluster_merge = (n_chunks > 1 && n_chunks <= AB_DECODE_MAX_CLUSTER) ? 1 : 0;
   dim3 grid(n_tokens, K * row_tiles, n_chunks);
 #define AB_GO(DM, NW)                                                                                               \
   {                                                                                                                 \
-    size_t tiles = (size_t)(16 + NW * 2 * 64) * pitch * sizeof(bf16);                                               \
-    size_t merge = (size_t)16 * pitch * sizeof(bf16) + (size_t)NW * 16 * (D + 2) * sizeof(float);                   \
+    size_t tiles = (size_t)(8 + NW * 2 * 16 * DECODE_RUN) * pitch * sizeof(bf16);                                   \
+    size_t merge = (size_t)8 * pitch * sizeof(bf16) + (size_t)(NW * 8 * (D + 6) + 8 * (D + 2)) * sizeof(float);     \
     size_t smem = tiles > merge ? tiles : merge;                                                                    \
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DM, NW>,                                           \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
-    ab_launch(attention_decode_kernel<DM, NW>, grid, dim3(NW * 32), smem, stream,                                   \
+    launch_clustered(attention_decode_kernel<DM, NW>, grid, dim3(NW * 32), smem, stream,                            \
+        cluster_merge ? (unsigned)n_chunks : 1u,                                                                    \
         (const bf16*)qkv, q_stride, (bf16*)out, part_o, part_ml, arrivals, (const bf16*)k_pages,                    \
         (const bf16*)v_pages, block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, pages_per_cta,        \
-        n_chunks);                                                                                                  \
+        n_chunks, cluster_merge);                                                                                   \
   }
-  if (n_chunks > 1 && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
+  if (n_chunks > AB_DECODE_MAX_CLUSTER && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
   switch (dmax_of(D)) {
-    case 64: if (small) AB_GO(64, 4) else AB_GO(64, 8) break;
-    case 128: if (small) AB_GO(128, 2) else AB_GO(128, 4) break;
-    default: AB_GO(256, 2); break;
+    case 64: AB_GO(64, 16); break;      // 16 warps x 13.5 KB
+    case 128: AB_GO(128, 8); break;     // 8 warps x 25.5 KB
+    default: AB_GO(256, 4); break;      // 4 warps x 49.5 KB
   }
 #undef AB_GO
+  (void)small;
   return ab_launch_status();
 }
 
@@ -698,11 +915,11 @@ AB_API int ab_attention_decode_bf16_noalloc(const void* qkv, int q_stride, void*
     return AB_BAD_ARG;
   }
   const unsigned long long partial = (unsigned long long)n_tokens * H * n_chunks * D;
-  const unsigned long long counters = (unsigned long long)n_tokens * K * ((H / K + 15) / 16);
+  const unsigned long long counters = (unsigned long long)n_tokens * K * ((H / K + 7) / 8);
   if (partial > AB_DECODE_NOALLOC_MAX_PARTIAL || counters > AB_DECODE_NOALLOC_MAX_COUNTERS) {
     snprintf(ab_noalloc_message, sizeof ab_noalloc_message,
              "problem too large for the built-in scratch: n_tokens*H*n_chunks*D = %llu (limit %u), "
-             "n_tokens*K*ceil(H/K/16) = %llu (limit %u); use ab_attention_decode_bf16 with scratch of your own",
+             "n_tokens*K*ceil(H/K/8) = %llu (limit %u); use ab_attention_decode_bf16 with scratch of your own",
              partial, AB_DECODE_NOALLOC_MAX_PARTIAL, counters, AB_DECODE_NOALLOC_MAX_COUNTERS);
     return AB_NOALLOC_TOO_LARGE;
   }

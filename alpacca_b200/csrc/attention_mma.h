@@ -23,7 +23,7 @@ extern "C" {
 // or allocating library routine.
 //
 // Limits: n_tokens * H * n_chunks * D <= AB_DECODE_NOALLOC_MAX_PARTIAL floats and
-// n_tokens * K * ceil(H / K / 16) <= AB_DECODE_NOALLOC_MAX_COUNTERS; larger problems
+// n_tokens * K * ceil(H / K / 8) <= AB_DECODE_NOALLOC_MAX_COUNTERS; larger problems
 // are refused with AB_NOALLOC_TOO_LARGE (the message of ab_attention_decode_bf16_noalloc_error
 // names the limit).  Use ab_attention_decode_bf16 with your own scratch for those.
 //

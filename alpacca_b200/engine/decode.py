@@ -55,10 +55,11 @@ def bucket_rows(n: int) -> int:
 
 
 def _width_bucket(pages: int) -> int:
-    w = 4
-    while w < pages:
-        w *= 2
-    return w
+    """Block-table width (pages per sequence) of the batch shape that holds sequences of `pages` pages."""
+    for b in (4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024):
+        if pages <= b:
+            return b
+    return -(-pages // 256) * 256
 
 
 class _Shape:

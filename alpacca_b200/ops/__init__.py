@@ -280,6 +280,7 @@ def _prefill_tiles(ctx, G, device, rows=64):
 
 
 _ARRIVALS: dict = {}
+DECODE_MAX_CLUSTER = 8           # chunks of one (sequence, head) that the decode attention merges in a cluster
 USE_TCGEN05_ATTENTION = True     # prefill steps of 128 tokens or more, head size 64: the tcgen05 kernel
 
 
@@ -320,18 +321,15 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
             _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0), _stream()), "attention_decode_wide")
         return out
     if ctx.is_decode:
-        # few pairs: a CTA per (sequence, head, chunk of pages), each warp one page at a time, two
-        # rounds per CTA; the chunks must cover the whole block table
+        # few pairs: a CTA per (sequence, head, chunk of pages).  A CTA covers `cap` pages per round;
+        # a table no wider than that is one CTA in one round, a wider one is 2 to 8 chunks merged
+        # inside a thread-block cluster, with as few rounds as that allows.
         small = 0
-        warps = lib.ab_attention_decode_warps(D, small)
-        pages_per_cta = 2 * warps
-        n_chunks = max(1, -(-table.shape[1] // pages_per_cta))
-        if n_chunks > 1:
-            part_o = torch.empty((T * H * n_chunks, D), dtype=torch.float32, device=qkv.device)
-            part_ml = torch.empty((T * H * n_chunks, 2), dtype=torch.float32, device=qkv.device)
-            arrivals = _arrival_counters(qkv.device, T * K * (-(-(H // K) // 16)))
-        else:
-            part_o = part_ml = arrivals = None
+        cap = lib.ab_attention_decode_round_pages(D)
+        width = max(int(table.shape[1]), 1)
+        n_chunks = min(DECODE_MAX_CLUSTER, -(-width // cap))
+        pages_per_cta = -(-width // (n_chunks * cap)) * cap
+        part_o = part_ml = arrivals = None
         _i32(ctx.tok_seq, T, "tok_seq")
         _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
         _check(lib.ab_attention_decode_bf16(

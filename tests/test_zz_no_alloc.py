@@ -44,12 +44,12 @@ def test_no_alloc_entry_point_matches_the_package_s_own():
     lib.ab_attention_decode_bf16_noalloc_error.restype = ctypes.c_char_p
     H, K, D = 8, 2, 64
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    ppc = 2 * lib.ab_attention_decode_warps(D, 0)
+    ppc = 2          # pages per chunk: more than 8 chunks, which are merged through the scratch memory
     for call, lengths in enumerate(([1500, 70, 2048, 1025], [900, 2047, 33, 1300])):   # several chunks each
         qkv, k, v, table, seq, lens = _setup(lengths, H, K, D, seed=call)
         B, W = table.shape
         n_chunks = -(-W // ppc)
-        assert n_chunks > 1, "the case must need the scratch memory"
+        assert n_chunks > 8, "the case must need the scratch memory"
         # the package's entry point, with scratch tensors of its caller
         want = torch.zeros(B, H * D, dtype=torch.bfloat16, device="cuda")
         part_o = torch.empty(B * H * n_chunks * D, dtype=torch.float32, device="cuda")
@@ -59,6 +59,13 @@ def test_no_alloc_entry_point_matches_the_package_s_own():
                                           _p(k), _p(v), _p(table), W, _p(seq), _p(lens), B, H, K, D,
                                           ctypes.c_float(D ** -0.5), 0, ppc, n_chunks, 0, stream)
         assert rc == 0
+        # few chunks, merged inside a cluster without scratch: the same result by another route
+        few = torch.zeros(B, H * D, dtype=torch.bfloat16, device="cuda")
+        rc = lib.ab_attention_decode_bf16(_p(qkv), qkv.shape[1], _p(few), None, None, None, _p(k), _p(v), _p(table),
+                                          W, _p(seq), _p(lens), B, H, K, D, ctypes.c_float(D ** -0.5), 0, 8,
+                                          -(-W // 8), 0, stream)
+        assert rc == 0
+        assert (few.float() - want.float()).abs().max().item() <= 1.6e-2
         # the entry point that allocates nothing: inputs and output only
         got = torch.zeros(B, H * D, dtype=torch.bfloat16, device="cuda")
         before = torch.cuda.memory_allocated()
