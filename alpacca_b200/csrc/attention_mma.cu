@@ -418,6 +418,63 @@ __device__ __forceinline__ void load_run_async(bf16* ks, bf16* vs, const bf16* _
   }
 }
 
+// Position rotation of one unit of 16 elements of a head (the same arithmetic, in the same order, as
+// the separate rotation kernel): unit u of a rotated head covers the pairs 8u .. 8u+7, i.e. with
+// pairing 0 (neighbours) the 16 consecutive elements from 16u, with pairing 1 (halves) the pieces at 8u
+// and n_rot/2 + 8u; units past n_rot / 16 and heads that are not rotated pass through.
+// (x0, x1) -> (x0 c - x1 s, x0 s + x1 c), alpacca/model.py:405-438.  Writes bfloat16 to dst.
+__device__ __forceinline__ void rotate_unit(const bf16* __restrict__ x, bf16* dst, int u, bool rotated,
+                                            const float* __restrict__ cos_row, const float* __restrict__ sin_row,
+                                            int n_rot, int pairing) {
+  const int rot_units = n_rot >> 4, half_r = n_rot >> 1;
+  const bool rotate = rotated && u < rot_units;
+  int ia, ib;
+  if (rotate && pairing == 1) { ia = 8 * u; ib = half_r + 8 * u; }
+  else if (rotate) { ia = 16 * u; ib = ia + 8; }
+  else { ia = rotated ? n_rot + 16 * (u - rot_units) : 16 * u; ib = ia + 8; }
+  uint4 ra = *reinterpret_cast<const uint4*>(x + ia), rb = *reinterpret_cast<const uint4*>(x + ib);
+  if (rotate) {
+    float c[8], sn[8], va[8], vb[8];
+    const float4 c0 = *reinterpret_cast<const float4*>(cos_row + 8 * u), c1 = *reinterpret_cast<const float4*>(cos_row + 8 * u + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sin_row + 8 * u), s1 = *reinterpret_cast<const float4*>(sin_row + 8 * u + 4);
+    c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      va[2 * i] = __uint_as_float(wa[i] << 16);
+      va[2 * i + 1] = __uint_as_float(wa[i] & 0xffff0000u);
+      vb[2 * i] = __uint_as_float(wb[i] << 16);
+      vb[2 * i + 1] = __uint_as_float(wb[i] & 0xffff0000u);
+    }
+    if (pairing == 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float x0 = va[j], x1 = vb[j];
+        va[j] = x0 * c[j] - x1 * sn[j];
+        vb[j] = x0 * sn[j] + x1 * c[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float* v = j < 4 ? va : vb;
+        const int e = 2 * (j & 3);
+        const float x0 = v[e], x1 = v[e + 1];
+        v[e] = x0 * c[j] - x1 * sn[j];
+        v[e + 1] = x0 * sn[j] + x1 * c[j];
+      }
+    }
+    ra = make_uint4(pack_bf16(va[0], va[1]), pack_bf16(va[2], va[3]), pack_bf16(va[4], va[5]), pack_bf16(va[6], va[7]));
+    rb = make_uint4(pack_bf16(vb[0], vb[1]), pack_bf16(vb[2], vb[3]), pack_bf16(vb[4], vb[5]), pack_bf16(vb[6], vb[7]));
+  }
+  *reinterpret_cast<uint4*>(dst + ia) = ra;
+  *reinterpret_cast<uint4*>(dst + ib) = rb;
+}
+
+// `fuse`: 0 = q is rotated and this step's key and value are in the cache already (the separate
+// rotation kernel ran); 1 = this kernel rotates q; the step's key and value are in the cache (a layer
+// that reads the cache of another); 2 = this kernel rotates q and k, takes this step's key and value
+// from qkv and writes them to their place in the cache.
 template <int DMAX, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
@@ -425,11 +482,13 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
                         const int* __restrict__ kv_len, int H, int K, int D, float scale_log2, int window,
-                        int pages_per_cta, int n_chunks, int cluster_merge) {
+                        int pages_per_cta, int n_chunks, int cluster_merge, bf16* k_out, bf16* v_out, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                        int n_rot, int pairing, int fuse) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch = D + 8;
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [8][pitch]
-  bf16* kv = qs + 8 * pitch;                                    // [NWARPS][2][16 * DECODE_RUN][pitch]
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [8][pitch] q, [2][pitch] this step's k, v
+  bf16* new_kv = qs + 8 * pitch;
+  bf16* kv = qs + 10 * pitch;                                   // [NWARPS][2][16 * DECODE_RUN][pitch]
 
   // What this kernel reads before the wait was written in earlier steps (lengths, block table,
   // every cached row but the one of this step's token), never by the kernels just before it.
@@ -474,7 +533,8 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
   cp_async_commit();
   pdl_wait();
   pdl_trigger();
-  if (pos >= t0 * 16 && pos < t1 * 16) {
+  const bool holds_new = active && chunk == last_chunk;        // this chunk ends with this step's token
+  if (fuse != 2 && pos >= t0 * 16 && pos < t1 * 16) {
     // the row that this step wrote
     const int tl = pos >> 4, r = pos & 15;
     const size_t base = ((size_t)bt[tl >> 2] * K + kh) * PAGE * D + (size_t)((tl & 3) * 16 + r) * D;
@@ -485,7 +545,7 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
     }
     cp_async_commit();
   }
-  {
+  if (!fuse) {
     const int cpr = D >> 3;
     for (int c = tid; c < 8 * cpr; c += NWARPS * 32) {
       const int r = c / cpr, cc = c - r * cpr;
@@ -494,8 +554,39 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
         v = *reinterpret_cast<const uint4*>(qkv + (size_t)tok * q_stride + (size_t)(kh * G + rt * 8 + r) * D + cc * 8);
       *reinterpret_cast<uint4*>(qs + r * pitch + cc * 8) = v;
     }
+  } else {
+    // rows 0..7: the tile's q heads, rotated (rows past the group: zero); rows 8, 9: this step's k
+    // (rotated) and v of this KV head, for the chunk that ends with them
+    const int upp = D >> 4;
+    const float* cos_row = cos_t ? cos_t + (size_t)pos * (n_rot >> 1) : nullptr;
+    const float* sin_row = sin_t ? sin_t + (size_t)pos * (n_rot >> 1) : nullptr;
+    const bf16* row = qkv + (size_t)tok * q_stride;
+    for (int it = tid; it < 10 * upp; it += NWARPS * 32) {
+      const int r = it / upp, u = it - r * upp;
+      if (r < n_heads) {
+        rotate_unit(row + (size_t)(kh * G + rt * 8 + r) * D, qs + r * pitch, u, cos_row != nullptr, cos_row, sin_row,
+                    n_rot, pairing);
+      } else if (r < 8) {
+        *reinterpret_cast<uint4*>(qs + r * pitch + 16 * u) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(qs + r * pitch + 16 * u + 8) = make_uint4(0, 0, 0, 0);
+      } else if (holds_new && fuse == 2) {
+        const bool is_k = r == 8;
+        rotate_unit(row + (size_t)(H + (is_k ? 0 : K) + kh) * D, new_kv + (r - 8) * pitch, u, is_k && cos_row != nullptr,
+                    cos_row, sin_row, n_rot, pairing);
+      }
+    }
   }
   __syncthreads();
+  if (fuse == 2 && holds_new && rt == 0) {
+    // this step's key and value go to their place in the cache (read by later steps)
+    const size_t base = (((size_t)bt[pos / PAGE] * K + kh) * PAGE + (pos % PAGE)) * D;
+    const int cpr = D >> 3;
+    for (int c = tid; c < 2 * cpr; c += NWARPS * 32) {
+      const int which = c / cpr, cc = c - which * cpr;
+      *reinterpret_cast<uint4*>((which ? v_out : k_out) + base + cc * 8) =
+          *reinterpret_cast<const uint4*>(new_kv + which * pitch + cc * 8);
+    }
+  }
   uint32_t qb[DMAX / 16][2];
 #pragma unroll
   for (int kd = 0; kd < DMAX / 16; ++kd) {
@@ -510,10 +601,18 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
     if (round > 0) {
       t0 = min(tile_end, tile_begin + (round * NWARPS + warp) * per_run);
       t1 = min(tile_end, t0 + per_run);
-      load_run_async(ks, vs, k_pages, v_pages, bt, K, kh, D, pitch, t0, t1, -1, lane);
+      load_run_async(ks, vs, k_pages, v_pages, bt, K, kh, D, pitch, t0, t1, fuse == 2 ? pos : -1, lane);
       cp_async_commit();
     }
     cp_async_wait<0>();
+    if (fuse == 2 && pos >= t0 * 16 && pos < t1 * 16) {
+      // this step's token lies in this run: its row comes from the staging rows, not from the cache
+      const int dst = (pos - t0 * 16) * pitch;
+      for (int cc = lane; cc < (D >> 3); cc += 32) {
+        *reinterpret_cast<uint4*>(ks + dst + cc * 8) = *reinterpret_cast<const uint4*>(new_kv + cc * 8);
+        *reinterpret_cast<uint4*>(vs + dst + cc * 8) = *reinterpret_cast<const uint4*>(new_kv + pitch + cc * 8);
+      }
+    }
     __syncwarp();
     if (t0 < t1) attend_run<DMAX>(st, qb, ks, vs, pitch, D, scale_log2, t1 - t0, t0 * 16, pos, lo);
     __syncwarp();      // every lane is done reading the run before the next one overwrites it
@@ -813,6 +912,13 @@ static inline cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, 
 
 #define AB_DECODE_MAX_CLUSTER 8
 
+AB_API int ab_attention_decode_rope_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
+                                         int* arrivals, void* k_pages, void* v_pages, const int* block_table,
+                                         int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
+                                         int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
+                                         int small, const float* cos_t, const float* sin_t, int n_rot, int pairing,
+                                         int fuse, cudaStream_t stream);
+
 // The chunks of one (token, KV head) are merged inside a thread-block cluster (through shared
 // memory) when there are 2 to 8 of them.  More chunks than that go through scratch memory:
 // part_o float [n_tokens * H * n_chunks, D], part_ml float [n_tokens * H * n_chunks, 2], arrivals int
@@ -823,9 +929,27 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
                                     int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
                                     int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
                                     int small, cudaStream_t stream) {
+  return ab_attention_decode_rope_bf16(qkv, q_stride, out, part_o, part_ml, arrivals, const_cast<void*>(k_pages),
+                                       const_cast<void*>(v_pages), block_table, table_width, tok_seq, kv_len,
+                                       n_tokens, H, K, D, scale, window, pages_per_cta, n_chunks, small, nullptr,
+                                       nullptr, 0, 0, 0, stream);
+}
+
+// The same with the position rotation and the append to the cache inside the kernel (`fuse` 1 or 2,
+// see the kernel; 0 is ab_attention_decode_bf16).  cos_t, sin_t: float [positions, n_rot / 2] or null
+// (no rotation); n_rot a multiple of 16; pairing 0 = neighbours, 1 = halves.
+AB_API int ab_attention_decode_rope_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
+                                         int* arrivals, void* k_pages, void* v_pages, const int* block_table,
+                                         int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
+                                         int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
+                                         int small, const float* cos_t, const float* sin_t, int n_rot, int pairing,
+                                         int fuse, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535 || pages_per_cta < 1)
     return AB_BAD_ARG;
+  if (fuse < 0 || fuse > 2 || n_rot < 0 || n_rot > D || (n_rot % 16) || pairing < 0 || pairing > 1) return AB_BAD_ARG;
+  if (!cos_t || !sin_t || fuse == 0) { cos_t = sin_t = nullptr; }
+  if (!cos_t) n_rot = 0;
   if ((long long)pages_per_cta * n_chunks < table_width) return AB_BAD_ARG;   // the chunks must cover the table
   const int G = H / K, row_tiles = (G + 7) / 8;
   if ((long long)K * row_tiles > 65535) return AB_BAD_ARG;
@@ -835,8 +959,8 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
   dim3 grid(n_tokens, K * row_tiles, n_chunks);
 #define AB_GO(DM, NW)                                                                                               \
   {                                                                                                                 \
-    size_t tiles = (size_t)(8 + NW * 2 * 16 * DECODE_RUN) * pitch * sizeof(bf16);                                   \
-    size_t merge = (size_t)8 * pitch * sizeof(bf16) + (size_t)(NW * 8 * (D + 6) + 8 * (D + 2)) * sizeof(float);     \
+    size_t tiles = (size_t)(10 + NW * 2 * 16 * DECODE_RUN) * pitch * sizeof(bf16);                                  \
+    size_t merge = (size_t)10 * pitch * sizeof(bf16) + (size_t)(NW * 8 * (D + 6) + 8 * (D + 2)) * sizeof(float);    \
     size_t smem = tiles > merge ? tiles : merge;                                                                    \
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DM, NW>,                                           \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
@@ -845,7 +969,7 @@ AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, fl
         cluster_merge ? (unsigned)n_chunks : 1u,                                                                    \
         (const bf16*)qkv, q_stride, (bf16*)out, part_o, part_ml, arrivals, (const bf16*)k_pages,                    \
         (const bf16*)v_pages, block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, pages_per_cta,        \
-        n_chunks, cluster_merge);                                                                                   \
+        n_chunks, cluster_merge, (bf16*)k_pages, (bf16*)v_pages, cos_t, sin_t, n_rot, pairing, fuse);               \
   }
   if (n_chunks > AB_DECODE_MAX_CLUSTER && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
   switch (dmax_of(D)) {

@@ -10,7 +10,10 @@
 // many bytes are in flight.  A CTA owns 16 weight rows and one of S slices of K
 // (grid N/16 x S); its 8 warps split the slice into runs, and every thread issues the loads
 // of up to 8 k-groups (256 bytes) before it consumes any, so a CTA of a
-// 2048-wide slice has all its 64 KB in flight at once.  S is chosen by the host
+// 2048-wide slice has all its 64 KB in flight at once.  A matrix with no more
+// 16-row slabs than the device has processors and a long K (the down projection)
+// gets CTAs of 16 warps instead: one CTA per processor either way, and half as
+// many rounds of loads one after the other.  S is chosen by the host
 // so that even a matrix of few rows gives a few CTAs to every processor.  The
 // weights do not depend on earlier kernels, so their loads are issued before the
 // wait of programmatic dependent launch and overlap the predecessor's tail.
@@ -95,12 +98,12 @@ __device__ __forceinline__ void epilogue(const float c[4], int i, int ln, int n0
   }
 }
 
-template <int NT, int EPI>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+template <int NT, int EPI, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias,
                  void* __restrict__ Y, float* __restrict__ partials, int* __restrict__ arrivals, int M, int N, int K,
                  int ldy, int groups_per_slice) {
-  __shared__ float red[GEMV_WARPS][NT][32][4];
+  __shared__ float red[WARPS][NT][32][4];
   __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -125,7 +128,7 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
   const int n_groups = (K + 31) / 32;
   const int slice_begin = slice * groups_per_slice;
   const int slice_end = min(n_groups, slice_begin + groups_per_slice);
-  const int per_warp = (slice_end - slice_begin + GEMV_WARPS - 1) / GEMV_WARPS;
+  const int per_warp = (slice_end - slice_begin + WARPS - 1) / WARPS;
   const int grp_begin = slice_begin + warp * per_warp;
   const int grp_end = min(slice_end, grp_begin + per_warp);
   bool waited = false;
@@ -178,7 +181,7 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
   float c[4] = {0.f, 0.f, 0.f, 0.f};
   if (finisher) {
 #pragma unroll
-    for (int w = 0; w < GEMV_WARPS; ++w)
+    for (int w = 0; w < WARPS; ++w)
 #pragma unroll
       for (int j = 0; j < 4; ++j) c[j] += red[w][i][ln][j];
   }
@@ -210,19 +213,28 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
 
 template <int EPI>
 static int launch(const void* X, const void* W, const float* bias, void* Y, float* partials, int* arrivals, int M,
-                  int N, int K, int ldy, int slices, cudaStream_t stream) {
+                  int N, int K, int ldy, int slices, int wide, cudaStream_t stream) {
   const int n_groups = (K + 31) / 32;
   const int gps = (n_groups + slices - 1) / slices;
   const dim3 grid((unsigned)((N + 15) / 16), (unsigned)((n_groups + gps - 1) / gps));
-  const dim3 block(GEMV_WARPS * 32);
-#define AB_GO(NT)                                                                                                  \
-  ab_launch(gemv_bf16_kernel<NT, EPI>, grid, block, 0, stream, (const bf16*)X, (const bf16*)W, bias, Y, partials,  \
-            arrivals, M, N, K, ldy, gps)
-  if (M <= 8) AB_GO(1);
-  else if (M <= 16) AB_GO(2);
-  else AB_GO(4);
+#define AB_GO(NT, WARPS)                                                                                           \
+  ab_launch(gemv_bf16_kernel<NT, EPI, WARPS>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)X, (const bf16*)W,   \
+            bias, Y, partials, arrivals, M, N, K, ldy, gps)
+  if (M <= 8) { if (wide) AB_GO(1, 16); else AB_GO(1, GEMV_WARPS); }
+  else if (M <= 16) AB_GO(2, GEMV_WARPS);
+  else AB_GO(4, GEMV_WARPS);
 #undef AB_GO
   return ab_launch_status();
+}
+
+static int gemv_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
 }
 
 // How many slices of K the host should ask for.  Measured on a B200 (2048x2048, 3072x2048,
@@ -244,10 +256,12 @@ AB_API int ab_gemv_bf16(const void* X, const void* W, const float* bias, void* Y
   if (M > 32 || K <= 0 || (K % 8) || slices < 1 || slices > 65535) return AB_BAD_ARG;
   if (slices > 1 && (!partials || !arrivals)) return AB_BAD_ARG;
   if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  // few slabs and more than one round of loads per warp: 16 warps per CTA
+  const int wide = (M <= 8 && slices == 1 && (N + 15) / 16 <= gemv_sm_count() && K > 8 * GEMV_U * 32) ? 1 : 0;
   switch (epilogue_kind) {
-    case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, stream);
-    case EPI_STORE_F32: return launch<EPI_STORE_F32>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, stream);
-    case EPI_SWIGLU_BF16: return launch<EPI_SWIGLU_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, stream);
+    case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, wide, stream);
+    case EPI_STORE_F32: return launch<EPI_STORE_F32>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, wide, stream);
+    case EPI_SWIGLU_BF16: return launch<EPI_SWIGLU_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, wide, stream);
   }
   return AB_BAD_ARG;
 }

@@ -298,6 +298,38 @@ def _arrival_counters(device, n: int):
     return buf
 
 
+def _decode_few(T, H, K, device) -> bool:
+    """Whether a decode step of T rows takes the kernel for few (sequence, head) pairs."""
+    return T * K * -(-(H // K) // 16) < 2 * _sm_count(device)
+
+
+def _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fuse=0):
+    """Decode attention for few (sequence, head) pairs: a CTA per (sequence, head, chunk of pages).
+    A CTA covers `cap` pages per round; a table no wider than that is one CTA in one round, a wider
+    one is 2 to 8 chunks merged inside a thread-block cluster, with as few rounds as that allows.
+    `fuse` 1: the kernel also rotates q; 2: it rotates q and k and appends k, v to the cache."""
+    lib = _lib("attention_mma")
+    k_pages, v_pages, table = cache.k, cache.v, cache.block_table
+    T = ctx.n_tokens
+    cos, sin, n_rot, pairing = rot if (rot is not None and fuse) else (None, None, 0, 0)
+    if cos is not None:
+        _cuda(cos, sin)
+        _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+              and sin.is_contiguous() and cos.shape == sin.shape and cos.shape[-1] == n_rot // 2 and n_rot % 16 == 0
+              and n_rot <= D, "rope tables must be float32 [P, n_rot/2], n_rot a multiple of 16")
+    cap = lib.ab_attention_decode_round_pages(D)
+    width = max(int(table.shape[1]), 1)
+    n_chunks = min(DECODE_MAX_CLUSTER, -(-width // cap))
+    pages_per_cta = -(-width // (n_chunks * cap)) * cap
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
+    _check(lib.ab_attention_decode_rope_bf16(
+        _p(qkv), qkv.shape[-1], _p(out), None, None, None, _p(k_pages), _p(v_pages), _p(table), table.shape[1],
+        _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0), pages_per_cta,
+        n_chunks, 0, _p(cos), _p(sin), n_rot, pairing, fuse, _stream()), "attention_decode")
+    return out
+
+
 def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
     """Tensor-core attention (bfloat16) over the paged cache; prefill or decode by the step's kind."""
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
@@ -312,7 +344,7 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
     _need(page == 64 and tuple(k_pages.shape[1:]) == (K, 64, D) and k_pages.shape == v_pages.shape
           and k_pages.is_contiguous() and v_pages.is_contiguous(), "attention_mma: cache pages [n_pages,K,64,D]")
     lib = _lib("attention_mma")
-    if ctx.is_decode and T * K * -(-(H // K) // 16) >= 2 * _sm_count(qkv.device):
+    if ctx.is_decode and not _decode_few(T, H, K, qkv.device):
         # many (sequence, head) pairs: one warp each, no merge and no scratch
         _i32(ctx.tok_seq, T, "tok_seq")
         _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
@@ -321,23 +353,7 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
             _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0), _stream()), "attention_decode_wide")
         return out
     if ctx.is_decode:
-        # few pairs: a CTA per (sequence, head, chunk of pages).  A CTA covers `cap` pages per round;
-        # a table no wider than that is one CTA in one round, a wider one is 2 to 8 chunks merged
-        # inside a thread-block cluster, with as few rounds as that allows.
-        small = 0
-        cap = lib.ab_attention_decode_round_pages(D)
-        width = max(int(table.shape[1]), 1)
-        n_chunks = min(DECODE_MAX_CLUSTER, -(-width // cap))
-        pages_per_cta = -(-width // (n_chunks * cap)) * cap
-        part_o = part_ml = arrivals = None
-        _i32(ctx.tok_seq, T, "tok_seq")
-        _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
-        _check(lib.ab_attention_decode_bf16(
-            _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(arrivals), _p(k_pages), _p(v_pages),
-            _p(table),
-            table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0),
-            pages_per_cta, n_chunks, small, _stream()), "attention_decode")
-        return out
+        return _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window)
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
     if USE_TCGEN05_ATTENTION and T >= 128 and qkv.shape[0] >= T:
@@ -366,6 +382,30 @@ def attention(qkv, out, cache, ctx, H, K, D, scale, window=0):
         return attention_mma(qkv, out, cache, ctx, H, K, D, scale, window)
     return attention_simt(qkv, out, cache.k, cache.v, cache.block_table, ctx.tok_pos, ctx.tok_seq,
                           ctx.n_tokens, H, K, D, scale, window)
+
+
+FUSE_ROPE_DECODE = True          # decode steps of few sequences: rotation and append inside the attention kernel
+
+
+def rope_attention(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, write_cache=True):
+    """Position rotation of q and k (`rot` = (cos, sin, n_rot, pairing) or None), append of k and v to
+    the cache (unless `write_cache` is off: a layer that reads another layer's cache), then attention
+    of the step's tokens over the cache.  Decode steps of few sequences in bfloat16 do all of it in
+    one kernel; everything else runs the rotation kernel and then `attention`."""
+    cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
+    T = ctx.n_tokens
+    if (FUSE_ROPE_DECODE and ctx.is_decode and qkv.dtype == torch.bfloat16 and D % 16 == 0 and D <= 256
+            and H // K <= 64 and n_rot % 16 == 0 and _decode_few(T, H, K, qkv.device)):
+        _cuda(qkv, out, cache.k, cache.v, cache.block_table)
+        _need(out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16 and qkv.is_contiguous()
+              and out.is_contiguous() and qkv.shape[-1] == (H + 2 * K) * D and out.numel() >= T * H * D
+              and H % K == 0, "rope_attention takes contiguous bfloat16 qkv [T,(H+2K)D], out [T,H*D]")
+        _need(tuple(cache.k.shape[1:]) == (K, 64, D) and cache.k.shape == cache.v.shape and cache.k.is_contiguous()
+              and cache.v.is_contiguous(), "rope_attention: cache pages [n_pages,K,64,D]")
+        return _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window, rot, 2 if write_cache else 1)
+    rope_append(qkv, cos, sin, ctx.tok_pos, ctx.tok_seq, cache.block_table, cache.k, cache.v, T, H, K, D, n_rot,
+                pairing, write_cache=write_cache)
+    return attention(qkv, out, cache, ctx, H, K, D, scale, window)
 
 
 def linear_bf16(x, w, out, n_rows=None, bias=None):

@@ -41,9 +41,7 @@ class Attention(Mixer):
         T = ctx.n_tokens
         qkv = self.qkv.forward(h, n_rows=T)
         rot = self.position.rotation() if self.position is not None else None
-        cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
-        ops.rope_append(qkv, cos, sin, ctx.tok_pos, ctx.tok_seq, cache.block_table, cache.k, cache.v,
-                        T, self.H, self.K, self.D, n_rot, pairing, write_cache=write_cache)
         att = torch.empty((h.shape[0], self.H * self.D), dtype=h.dtype, device=h.device)
-        ops.attention(qkv, att, cache, ctx, self.H, self.K, self.D, self.scale, self.window or 0)
+        ops.rope_attention(qkv, att, cache, ctx, self.H, self.K, self.D, self.scale, self.window or 0, rot,
+                           write_cache=write_cache)
         return self.out.forward(att, n_rows=T)

@@ -445,3 +445,41 @@ def test_attention_prefill_tcgen05(H, K, window):
         close(got[t0:t0 + ql].view(ql, H, D), want, "bfloat16", f"tcgen05, sequence {b}")
         close(other[t0:t0 + ql].view(ql, H, D), want, "bfloat16", f"mma.sync, sequence {b}")
         t0 += ql
+
+
+@pytest.mark.parametrize("H,K,D,n_rot,pairing", [(4, 4, 16, 16, 0), (6, 2, 32, 32, 1), (10, 5, 48, 32, 1),
+                                                 (32, 8, 64, 64, 1), (4, 2, 128, 64, 0), (40, 2, 64, 0, 0)])
+@pytest.mark.parametrize("window", [0, 130])
+@pytest.mark.parametrize("write_cache", [True, False])
+def test_rope_attention_fused_decode(H, K, D, n_rot, pairing, window, write_cache):
+    """Rotation, append and attention of a decode step in one kernel against the two kernels one
+    after the other: the same outputs and the same cache, bit for bit; one to several chunks."""
+    from alpacca_b200 import ops
+    from alpacca_b200.cache import KVLayerView
+    lengths = [1, 64, 65, 300, 769, 1025, 1600]
+    B = len(lengths)
+    qkv0 = rnd(B, (H + 2 * K) * D, dtype=torch.bfloat16, seed=17)
+    ang = rnd(1700, max(n_rot // 2, 1), seed=5, scale=3.0)
+    rot = (torch.cos(ang).contiguous(), torch.sin(ang).contiguous(), n_rot, pairing) if n_rot else None
+    results = []
+    for fused in (False, True):
+        table, kp, vp = make_paged(lengths, 70, K, D, torch.bfloat16, seed=D + H)
+        for b, n in enumerate(lengths):
+            # with write_cache off the step's own row is in the cache already (another layer's)
+            fill_cache(table.cpu(), kp, vp, b, rnd(n, K, D, dtype=torch.bfloat16, seed=18 + b),
+                       rnd(n, K, D, dtype=torch.bfloat16, seed=31 + b))
+        ctx = decode_ctx(lengths)
+        ctx.tok_seq[2] = -1                      # a padding row: no output, nothing appended
+        qkv = qkv0.clone()
+        out = torch.full((B, H * D), 7.0, dtype=torch.bfloat16, device="cuda")
+        ops.FUSE_ROPE_DECODE = fused
+        try:
+            ops.rope_attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, window, rot,
+                               write_cache=write_cache)
+        finally:
+            ops.FUSE_ROPE_DECODE = True
+        results.append((out, kp, vp))
+    (o1, k1, v1), (o2, k2, v2) = results
+    assert torch.equal(o1, o2), f"outputs differ by {(o1.float() - o2.float()).abs().max().item()}"
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert (o1[3].float().abs() > 0).any() and torch.equal(o1[2], torch.full_like(o1[2], 7.0))
