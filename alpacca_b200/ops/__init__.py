@@ -305,8 +305,8 @@ def _decode_few(T, H, K, device) -> bool:
 
 def _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fuse=0):
     """Decode attention for few (sequence, head) pairs: a CTA per (sequence, head, chunk of pages).
-    A CTA covers `cap` pages per round; a table no wider than that is one CTA in one round, a wider
-    one is 2 to 8 chunks merged inside a thread-block cluster, with as few rounds as that allows.
+    A CTA covers `cap` pages per round; wide tables are cut into 2 to 8 chunks that are merged inside
+    a thread-block cluster.
     `fuse` 1: the kernel also rotates q; 2: it rotates q and k and appends k, v to the cache."""
     lib = _lib("attention_mma")
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
@@ -319,8 +319,18 @@ def _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window, rot=None
               and n_rot <= D, "rope tables must be float32 [P, n_rot/2], n_rot a multiple of 16")
     cap = lib.ab_attention_decode_round_pages(D)
     width = max(int(table.shape[1]), 1)
-    n_chunks = min(DECODE_MAX_CLUSTER, -(-width // cap))
-    pages_per_cta = -(-width // (n_chunks * cap)) * cap
+    # A second round in the same CTA costs less than a cluster of two (measured: about 2 against 3
+    # microseconds), and rounds are only run for keys that exist; so one CTA up to two rounds' worth
+    # of table, beyond that as few chunks as two rounds each allow, or more of them (one round each at
+    # most) while they still find processors of their own.
+    n_chunks = -(-width // (2 * cap))
+    if n_chunks > 1:
+        pairs = T * K * -(-(H // K) // 8)
+        most = min(DECODE_MAX_CLUSTER, -(-width // cap))
+        n_chunks = min(n_chunks, DECODE_MAX_CLUSTER)
+        while n_chunks < most and pairs * (n_chunks + 1) <= _sm_count(qkv.device):
+            n_chunks += 1
+    pages_per_cta = -(-width // n_chunks)
     _i32(ctx.tok_seq, T, "tok_seq")
     _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
     _check(lib.ab_attention_decode_rope_bf16(

@@ -150,6 +150,9 @@ def measure_decode(model, batch, steps, warmup, seed=0):
     from alpacca_b200 import ops
     slots, decoder, live = start_batch(model, batch, seed)
     try:
+        # the pages of the whole run are reserved first, so that the warm-up steps and the timed
+        # steps have the same batch shape (and the capture of its graph falls into the warm-up)
+        model.engine.cache.reserve([(s, max(warmup, 3) + steps) for s in slots])
         decoder.run(live, max(warmup, 3))
         before = ops.launches
         torch.cuda.synchronize()
