@@ -1,8 +1,12 @@
 """Decode steps (one token per sequence) for the generation loop.
 
-Two decoders with one interface, `step(live) -> tokens`, where `live` lists
-(slot, token to feed, sampler state) of the sequences still running and the
-result is the next token of each:
+Two decoders with one interface, `step(live, more=None, stop=()) -> tokens`,
+where `live` lists (slot, token to feed, sampler state) of the sequences still
+running and the result is the next token of each.  `more[i]` says whether
+sequence i has room for yet another step after this one, and `stop` holds the
+tokens that end a sequence: with them a decoder knows, as soon as it has this
+step's tokens, which sequences the caller will bring back, and may start their
+next step before it returns (the caller must then come back with exactly those).
 
   EagerDecoder   one `Engine.step` and one sampler call per step; works for any model.
   GraphDecoder   the whole step - embedding to sampled token, and the feeding
@@ -30,7 +34,7 @@ class EagerDecoder:
     def __init__(self, engine, sampler):
         self.engine, self.sampler = engine, sampler
 
-    def step(self, live):
+    def step(self, live, more=None, stop=()):
         logits = self.engine.step([StepEntry(slot, [tok], [0]) for slot, tok, _ in live])
         return self.sampler.sample(logits, [st for _, _, st in live])
 
@@ -87,7 +91,7 @@ class _Shape:
         o, n = self.sect["tok_seq"]
         self.mask_host, self.mask_dev = self.host[o:o + n], self.dev[o:o + n]   # the live mask of the rows
         self.sampled = torch.zeros(rows, dtype=torch.int32, device=dev)
-        self.sampled_host = torch.zeros(rows, dtype=torch.int32, pin_memory=True)
+        self.sampled_hosts = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.history = torch.zeros((dec.history_len, rows), dtype=torch.int32, device=dev)
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.graph = None
@@ -132,6 +136,8 @@ class GraphDecoder:
         self.expect: dict = {}          # slot -> (length, last sampled token) after the last step
         self.pages_seen = -1
         self._last_slots, self._last_rows, self._room = None, None, 0
+        self._flights: list = []        # steps that run ahead of the caller, oldest first
+        self._buf = 0
 
     # -- the captured step -------------------------------------------------------------
     def _body(self, sh: _Shape):
@@ -303,19 +309,73 @@ class GraphDecoder:
         self.expect = {slot: (cache.length(slot), None) for slot, _, _ in live}
         return rows
 
-    def step(self, live):
-        """One step: the live mask goes to the device (a small copy from pinned memory), the graph
-        is replayed, the sampled tokens come back."""
+    def _launch(self, live):
+        """Enqueues one step for `live` and the read-back of its tokens into a pinned buffer of its own."""
         rows = self.run(live, 1, always_mask=True)
         sh = self.shape
-        sh.sampled_host.copy_(sh.sampled, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        got = sh.sampled_host.tolist()
-        tokens = [got[r] for r in rows]
+        self._buf ^= 1
+        host = sh.sampled_hosts[self._buf]
+        host.copy_(sh.sampled, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return {"live": list(live), "rows": rows, "done": done, "host": host}
+
+    def _drop_flights(self, live):
+        """Gives up the steps that ran ahead for sequences the caller did not bring back: their tokens
+        are dropped, the lengths they were counted with are taken back, the device state is uploaded
+        anew by the next step."""
+        flights, self._flights = self._flights, []
+        flights[-1]["done"].synchronize()
+        # a sequence is known by its sampler state: one that the caller still brings has the steps
+        # that ran ahead in its length; one that is gone has given its slot back
+        here = {id(st) for _, _, st in live}
+        for f in flights:
+            self.engine.cache.commit([(slot, -1) for slot, _, st in f["live"] if id(st) in here])
+        sampler = self.sampler
+        self.reset()
+        self.sampler = sampler
+
+    def settle(self, live) -> None:
+        """Gives up the steps that run ahead, if there are any (`live`: the sequences still running,
+        as they would be brought to the next step), so that lengths are what the caller has seen."""
+        if self._flights:
+            self._drop_flights(live)
+
+    def step(self, live, more=None, stop=()):
+        """One step: the live mask goes to the device (a small copy from pinned memory), the graph
+        is replayed, the sampled tokens come back.
+
+        With `more`, up to two further steps are enqueued before this step's tokens are returned, so
+        that the device never waits for the host: the next step of all sequences that have room for
+        one is enqueued before this step's tokens are even known (it feeds on the tokens on the
+        device), provided that needs nothing from the host but the replay.  If one of them then
+        samples a stop token, the caller comes back without it, and the step that ran ahead is given
+        up: one step's worth of device time for each sequence end by a stop token."""
+        q = self._flights
+        if q and [(slot, tok) for slot, tok, _ in q[0]["live"]] != [(slot, tok) for slot, tok, _ in live]:
+            self._drop_flights(live)
+            q = self._flights
+        if not q:
+            q.append(self._launch(live))
+        slots = [slot for slot, _, _ in live]
+        if more is not None and len(q) == 1 and all(more) and slots == self._last_slots and self._room >= 1:
+            q.append(self._launch([(slot, None, st) for slot, _, st in live]))
+        flight = q.pop(0)
+        flight["done"].synchronize()
+        got = flight["host"].tolist()
+        tokens = [got[r] for r in flight["rows"]]
         for (slot, _, st), t in zip(live, tokens):
             st.step += 1
             st.accept(t)
-            self.expect[slot] = (self.expect[slot][0], t)
+            if not q:
+                self.expect[slot] = (self.expect[slot][0], t)
+        if q:
+            # the step that ran ahead fed on these tokens
+            q[0]["live"] = [(slot, t, st) for (slot, _, st), t in zip(live, tokens)]
+        elif more is not None:
+            ahead = [(slot, t, st) for (slot, _, st), t, m in zip(live, tokens, more) if m and t not in stop]
+            if ahead:
+                q.append(self._launch(ahead))
         return tokens
 
     def history(self, n_steps: int, n_live: int) -> torch.Tensor:
@@ -330,6 +390,9 @@ class GraphDecoder:
         another sampler with the same options but its own seed."""
         if sampler is not None:
             self.sampler = sampler
+        if self._flights:
+            self._flights[-1]["done"].synchronize()
+            self._flights = []
         self.shape, self.layout, self.row_of, self.mask, self.pages_seen = None, [], {}, [], -1
         self.expect = {}
         self._last_slots, self._last_rows, self._room = None, None, 0

@@ -40,6 +40,11 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def wait(self) -> None:
+        """Returns when every step issued so far has run (steps are issued asynchronously)."""
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+
     def room_for(self, token_counts) -> bool:
         """Whether new sequences of these lengths fit together into what is free now."""
         pages = sum(-(-int(n) // 64) for n in token_counts)

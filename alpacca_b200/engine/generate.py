@@ -13,7 +13,8 @@ when the batch is done the next requests form the next batch, until none are
 left.  Nothing joins a batch that has started.
 
 The loop decides; it does not compute.  It needs of the engine only
-`alloc_slot`, `free_slot`, `step`, `length`, `max_positions` and `room_for`,
+`alloc_slot`, `free_slot`, `step`, `length`, `max_positions` and `room_for`
+(and `wait`, if it has one),
 and of the sampler only `new_state` and `sample`, so its decisions are tested
 on the CPU with stand-ins for both.
 """
@@ -72,8 +73,8 @@ def generate_requests(engine, sampler, prompts, n_predict: int = -1, stop_token_
     """Generates for every prompt (a list of token ids); returns results in the order of the prompts.
 
     `on_token(request index, token)` is called for every token that is kept.  `decoder` runs the
-    single-token steps (`step(live) -> tokens`, see engine/decode.py); by default every step is one
-    `engine.step` and one `sampler.sample`.
+    single-token steps (`step(live, more, stop) -> tokens`, see engine/decode.py); by default every
+    step is one `engine.step` and one `sampler.sample`.
     """
     if decoder is None:
         from .decode import EagerDecoder
@@ -94,7 +95,12 @@ def generate_requests(engine, sampler, prompts, n_predict: int = -1, stop_token_
         live = list(batch)
         try:
             logits = engine.step([StepEntry(slots[i], prompts[i], [len(prompts[i]) - 1]) for i in live])
+            if hasattr(engine, "wait"):
+                engine.wait()       # the clock starts when the prompt has been evaluated (alpacca/chat.py:153-157)
             t0 = timer()
+            # tokens in the cache after the prompt; with k tokens sampled and all but the last fed
+            # back a sequence holds base + k - 1 (the decoder may already be a step further)
+            base = {i: engine.length(slots[i]) for i in live}
 
             def finish(i, reason):
                 results[i].finish_reason = reason
@@ -127,14 +133,18 @@ def generate_requests(engine, sampler, prompts, n_predict: int = -1, stop_token_
                         on_token(i, tok)
                     if res.tokens >= budgets[i]:
                         finish(i, "length")
-                    elif engine.length(slots[i]) + 1 >= max_pos:
+                    elif base[i] + res.tokens >= max_pos:
                         finish(i, "context")
                     else:
                         entries.append((slots[i], tok, states[i]))
                         nxt.append(i)
                 live = nxt
                 if live:
-                    tokens = decoder.step(entries)
+                    # whether a sequence has room for one more step after this one (the two tests
+                    # above, one token further), unless a stop token ends it
+                    more = [results[i].tokens + 1 < budgets[i] and base[i] + results[i].tokens + 1 < max_pos
+                            for i in live]
+                    tokens = decoder.step(entries, more, stop)
         finally:
             for s in slots.values():
                 engine.free_slot(s)

@@ -143,3 +143,33 @@ def test_on_token_and_slot_release_on_error():
     with pytest.raises(RuntimeError):
         generate_requests(eng, GreedySampler(), [[1], [2]], 5, ())
     assert eng.lengths == {}, "slots must come back when a step fails"
+
+
+def test_the_loop_tells_the_decoder_who_comes_back():
+    """`more` and `stop` let a decoder know, from a step's tokens alone, which sequences the loop
+    brings to the next step (it may start that step early): the forecast must be exact, whatever
+    ends a sequence (budget, context, stop token)."""
+    from alpacca_b200.engine.decode import EagerDecoder
+
+    class Forecasting(EagerDecoder):
+        forecast = None
+        calls = 0
+
+        def step(self, live, more=None, stop=()):
+            assert more is not None and len(more) == len(live)
+            if self.forecast is not None:
+                assert [(slot, tok) for slot, tok, _ in live] == self.forecast
+            tokens = super().step(live)
+            self.forecast = [(slot, t) for (slot, _, _), t, m in zip(live, tokens, more) if m and t not in stop]
+            type(self).calls += 1
+            return tokens
+
+    for kw in (dict(n_predict=5, stop=()), dict(n_predict=-1, stop=()), dict(n_predict=9, stop=(9, 14))):
+        eng = FakeEngine(max_positions=12)
+        dec = Forecasting(eng, GreedySampler())
+        res = generate_requests(eng, dec.sampler, [[3, 4], [7], [10, 11, 12, 13, 1]], kw["n_predict"], kw["stop"],
+                                decoder=dec)
+        assert dec.forecast == [], "the last step must forecast that nobody comes back"
+        assert eng.lengths == {}
+        assert [r.finish_reason for r in res] != []
+    assert Forecasting.calls > 10

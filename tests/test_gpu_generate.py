@@ -147,3 +147,52 @@ def test_graph_and_eager_decoding_agree_over_many_steps(model_dirs):
     assert out[True] == out[False]
     assert len({len(t) for t, _ in out[True]}) > 1, "the sequences should end at different times"
     assert out[False][1][0] == free[1].token_ids[:len(out[False][1][0])]
+
+
+def runs_len_hint(trace, prompts):
+    """Lengths of sequences 0 and 2 after the prompt and len(trace) - 1 fed tokens."""
+    return [len(prompts[0]) + len(trace) - 1, len(prompts[2]) + len(trace) - 1]
+
+
+def test_a_step_that_ran_ahead_is_given_up_cleanly(model_dirs):
+    """The graph decoder starts the next step early when it is told who comes back.  A caller that
+    comes back with other sequences, or other tokens, than forecast gets what it asked for: the early
+    step is dropped, lengths and device state are put right, and the tokens are those of the plain
+    step-by-step decoder."""
+    import torch
+    from alpacca_b200.api import Model
+    from alpacca_b200.engine.decode import EagerDecoder
+    from alpacca_b200.engine.step import StepEntry
+    from alpacca_b200.sampling import DeviceSampler, SamplerParams
+    d = model_dirs[("b", "bfloat16")]
+    prompts = [tiny.prompt_tokens(tiny.TINY_B, n, 900 + i) for i, n in enumerate((5, 70, 33))]
+    runs = {}
+    for kind in ("graph", "eager"):
+        model = Model.load(d, dtype="bfloat16", max_batch=4)
+        eng = model.engine
+        sampler = DeviceSampler(SamplerParams.greedy(), eng.device)
+        dec = model.decoder_for(sampler) if kind == "graph" else EagerDecoder(eng, sampler)
+        slots = [eng.alloc_slot() for _ in prompts]
+        states = [sampler.new_state(i, p) for i, p in enumerate(prompts)]
+        logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        toks = sampler.sample(logits, states)
+        trace = [list(toks)]
+        live = [(s, t, st) for s, t, st in zip(slots, toks, states)]
+        for step in range(12):
+            toks = dec.step(live, more=[True] * len(live), stop=())
+            trace.append(list(toks))
+            live = [(s, t, st) for (s, _, st), t in zip(live, toks)]
+            if step == 3:            # one sequence leaves although it was forecast to stay
+                eng.free_slot(live[1][0])
+                live = [live[0], live[2]]
+            if step == 7:            # another token than the sampled one is fed
+                live[0] = (live[0][0], (live[0][1] + 1) % tiny.TINY_B["vocab_size"], live[0][2])
+        if kind == "graph":
+            assert [eng.length(s) for s, _, _ in live] > runs_len_hint(trace, prompts)
+            dec.settle(live)         # steps that run ahead are in the lengths until they are given up
+        runs[kind] = (trace, [eng.length(s) for s, _, _ in live])
+        for s, _, _ in live:
+            eng.free_slot(s)
+        assert eng.cache.slots.n_held == 0
+        torch.cuda.synchronize()
+    assert runs["graph"] == runs["eager"]
