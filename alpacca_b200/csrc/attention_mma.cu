@@ -737,119 +737,23 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
 }
 
 // ---------------------------------------------------------------------------
-// decode for many sequences: one WARP per (sequence, KV head, row tile).  The warp walks the
-// sequence's pages one after another with two tiles of its own in shared memory (the next page is
-// on its way while the current one is consumed).  Nothing is shared between warps: no merge, no
-// scratch.  With hundreds of (sequence, head) pairs this keeps every SM streaming; with few pairs
-// the CTA-per-pair kernel above has the shorter chain.
-// ---------------------------------------------------------------------------
-template <int DMAX, int NWARPS>
-__global__ void __launch_bounds__(NWARPS * 32)
-attention_decode_wide_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
-                             const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
-                             const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
-                             const int* __restrict__ kv_len, int n_tokens, int H, int K, int D, float scale_log2,
-                             int window) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int pitch = D + 8;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t4 = lane & 3;
-  const int G = H / K;
-  const int row_tiles = (G + 15) / 16;
-  // per warp: q [16][pitch], then 2 x (k [64][pitch], v [64][pitch])
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * (16 + 4 * 64) * pitch;
-  bf16* kv = qs + 16 * pitch;
-
-  const long long pair = (long long)blockIdx.x * NWARPS + warp;
-  const long long n_pairs = (long long)n_tokens * K * row_tiles;
-  const bool exists = pair < n_pairs;
-  const int tok = exists ? (int)(pair / (K * row_tiles)) : 0;
-  const int rem = exists ? (int)(pair - (long long)tok * (K * row_tiles)) : 0;
-  const int kh = rem / row_tiles, rt = rem - kh * row_tiles;
-  const int* bt = block_table + (size_t)tok * table_width;
-  const int b = exists ? tok_seq[tok] : -1;
-  const int len = exists ? kv_len[tok] : 0;
-  const bool live = b >= 0;
-  const int pos = len - 1;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int first_page = lo / PAGE, last_page = pos / PAGE;
-  const int n_tiles = live ? last_page - first_page + 1 : 0;
-  const int n_rows = min(16, G - rt * 16);
-
-  auto load_page = [&](int i) {               // tile i -> buffer i & 1
-    const size_t base = ((size_t)bt[first_page + i] * K + kh) * PAGE * D;
-    bf16* dst = kv + (size_t)(i & 1) * 2 * 64 * pitch;
-    load_tile_async(dst, k_pages + base, D, pitch, lane, 32);
-    load_tile_async(dst + 64 * pitch, v_pages + base, D, pitch, lane, 32);
-  };
-  // pages written in earlier steps may be fetched before the wait; the last page holds this step's token
-  bool waited = false;
-  if (n_tiles > 1) load_page(0);
-  cp_async_commit();
-  pdl_wait();
-  pdl_trigger();
-  waited = true;
-  if (n_tiles == 1) load_page(0);
-  cp_async_commit();
-  if (!live) return;
-  {
-    const int cpr = D >> 3;
-    for (int c = lane; c < 16 * cpr; c += 32) {
-      const int r = c / cpr, cc = c - r * cpr;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < n_rows)
-        v = *reinterpret_cast<const uint4*>(qkv + (size_t)tok * q_stride + (size_t)(kh * G + rt * 16 + r) * D + cc * 8);
-      *reinterpret_cast<uint4*>(qs + r * pitch + cc * 8) = v;
-    }
-  }
-  RowState<DMAX> st;
-  init_state(st);
-  for (int i = 0; i < n_tiles; ++i) {
-    if (i + 1 < n_tiles) load_page(i + 1);     // into the buffer that tile i-1 left
-    cp_async_commit();
-    cp_async_wait<1>();                        // tile i has landed
-    __syncwarp();
-    const bf16* ks = kv + (size_t)(i & 1) * 2 * 64 * pitch;
-    const int key0 = (first_page + i) * PAGE;
-    const bool need_mask = (key0 + PAGE - 1 > pos) || (key0 < lo);
-    attend_tile<DMAX>(st, qs, ks, ks + 64 * pitch, pitch, D, scale_log2, key0, pos, pos, lo, lo, need_mask);
-    __syncwarp();                              // all lanes are done with the tile before it is overwritten
-  }
-  (void)waited;
-  float l0 = st.l[0], l1 = st.l[1];
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
-#pragma unroll
-  for (int dt = 0; dt < DMAX / 8; ++dt) {
-    if (dt * 8 < D) {
-      const int d = dt * 8 + 2 * t4;
-      if (g < n_rows)
-        *reinterpret_cast<uint32_t*>(out + ((size_t)tok * H + kh * G + rt * 16 + g) * D + d) =
-            pack_bf16(st.o[dt][0] * inv0, st.o[dt][1] * inv0);
-      if (g + 8 < n_rows)
-        *reinterpret_cast<uint32_t*>(out + ((size_t)tok * H + kh * G + rt * 16 + g + 8) * D + d) =
-            pack_bf16(st.o[dt][2] * inv1, st.o[dt][3] * inv1);
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------
 // entry points
 // ---------------------------------------------------------------------------
 static int dmax_of(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : 256); }
 
-// warps of a decode CTA for head size D (`small` is ignored: there is one CTA size per head size)
+// warps of a decode CTA for head size D; `small` (0, 1, 2) halves the CTA that many times: with
+// many (sequence, head) pairs several small CTAs per processor do better than one large one
 AB_API int ab_attention_decode_warps(int D, int small) {
-  (void)small;
   const int dm = dmax_of(D);
-  return dm == 64 ? 16 : (dm == 128 ? 8 : 4);
+  const int full = dm == 64 ? 16 : (dm == 128 ? 8 : 4);
+  return full >> (small < 0 ? 0 : (small > 2 ? 2 : small));
 }
 
-// pages that a decode CTA covers in one round: its warps' runs of DECODE_RUN tiles of 16 keys
-AB_API int ab_attention_decode_round_pages(int D) { return ab_attention_decode_warps(D, 0) * DECODE_RUN * 16 / PAGE; }
+// keys that a decode CTA covers in one round: its warps' runs of DECODE_RUN tiles of 16 keys
+AB_API int ab_attention_decode_round_keys(int D, int small) {
+  return ab_attention_decode_warps(D, small) * DECODE_RUN * 16;
+}
+AB_API int ab_attention_decode_round_pages(int D) { return ab_attention_decode_round_keys(D, 0) / PAGE; }
 
 AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
                                      const void* v_pages, const int* block_table, int table_width,
@@ -947,6 +851,7 @@ AB_API int ab_attention_decode_rope_bf16(const void* qkv, int q_stride, void* ou
   if (n_tokens <= 0) return AB_OK;
   if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535 || pages_per_cta < 1)
     return AB_BAD_ARG;
+  if (small < 0 || small > 2) return AB_BAD_ARG;
   if (fuse < 0 || fuse > 2 || n_rot < 0 || n_rot > D || (n_rot % 16) || pairing < 0 || pairing > 1) return AB_BAD_ARG;
   if (!cos_t || !sin_t || fuse == 0) { cos_t = sin_t = nullptr; }
   if (!cos_t) n_rot = 0;
@@ -973,40 +878,16 @@ AB_API int ab_attention_decode_rope_bf16(const void* qkv, int q_stride, void* ou
   }
   if (n_chunks > AB_DECODE_MAX_CLUSTER && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
   switch (dmax_of(D)) {
-    case 64: AB_GO(64, 16); break;      // 16 warps x 13.5 KB
-    case 128: AB_GO(128, 8); break;     // 8 warps x 25.5 KB
-    default: AB_GO(256, 4); break;      // 4 warps x 49.5 KB
-  }
-#undef AB_GO
-  (void)small;
-  return ab_launch_status();
-}
-
-AB_API int ab_attention_decode_wide_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
-                                         const void* v_pages, const int* block_table, int table_width,
-                                         const int* tok_seq, const int* kv_len, int n_tokens, int H, int K, int D,
-                                         float scale, int window, cudaStream_t stream) {
-  if (n_tokens <= 0) return AB_OK;
-  if (D <= 0 || D > 256 || (D % 16) || H % K) return AB_BAD_ARG;
-  const int G = H / K, row_tiles = (G + 15) / 16;
-  const long long pairs = (long long)n_tokens * K * row_tiles;
-  const int pitch = D + 8;
-  const float sl = scale * LOG2E;
-#define AB_GO(DM, NW)                                                                                               \
-  {                                                                                                                 \
-    const size_t smem = (size_t)NW * (16 + 4 * 64) * pitch * sizeof(bf16);                                          \
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_wide_kernel<DM, NW>,                                      \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
-    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
-    const unsigned blocks = (unsigned)((pairs + NW - 1) / NW);                                                      \
-    ab_launch(attention_decode_wide_kernel<DM, NW>, dim3(blocks), dim3(NW * 32), smem, stream,                      \
-        (const bf16*)qkv, q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages, block_table,           \
-        table_width, tok_seq, kv_len, n_tokens, H, K, D, sl, window);                                               \
-  }
-  switch (dmax_of(D)) {
-    case 64: AB_GO(64, 4); break;       // 4 warps x 39 KB
-    case 128: AB_GO(128, 2); break;     // 2 warps x 74 KB
-    default: AB_GO(256, 1); break;      // 1 warp x 144 KB
+    // warps x shared memory of a warp's run of keys and values; `small` halves the CTA once or twice
+    case 64:                            // 16 warps x 13.5 KB
+      if (small == 0) AB_GO(64, 16) else if (small == 1) AB_GO(64, 8) else AB_GO(64, 4)
+      break;
+    case 128:                           // 8 warps x 25.5 KB
+      if (small == 0) AB_GO(128, 8) else if (small == 1) AB_GO(128, 4) else AB_GO(128, 2)
+      break;
+    default:                            // 4 warps x 49.5 KB
+      if (small == 0) AB_GO(256, 4) else if (small == 1) AB_GO(256, 2) else AB_GO(256, 1)
+      break;
   }
 #undef AB_GO
   return ab_launch_status();

@@ -298,15 +298,11 @@ def _arrival_counters(device, n: int):
     return buf
 
 
-def _decode_few(T, H, K, device) -> bool:
-    """Whether a decode step of T rows takes the kernel for few (sequence, head) pairs."""
-    return T * K * -(-(H // K) // 16) < 2 * _sm_count(device)
-
-
-def _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fuse=0):
-    """Decode attention for few (sequence, head) pairs: a CTA per (sequence, head, chunk of pages).
-    A CTA covers `cap` pages per round; wide tables are cut into 2 to 8 chunks that are merged inside
-    a thread-block cluster.
+def _attention_decode(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fuse=0):
+    """Decode attention: a CTA per (sequence, KV head, chunk of pages).  With few (sequence, head)
+    pairs a CTA is large and a long table is cut into 2 to 8 chunks that are merged inside a
+    thread-block cluster; with more pairs than processors the CTAs are smaller (several per
+    processor) and each walks its whole table in rounds.
     `fuse` 1: the kernel also rotates q; 2: it rotates q and k and appends k, v to the cache."""
     lib = _lib("attention_mma")
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
@@ -317,26 +313,30 @@ def _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window, rot=None
         _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
               and sin.is_contiguous() and cos.shape == sin.shape and cos.shape[-1] == n_rot // 2 and n_rot % 16 == 0
               and n_rot <= D, "rope tables must be float32 [P, n_rot/2], n_rot a multiple of 16")
-    cap = lib.ab_attention_decode_round_pages(D)
     width = max(int(table.shape[1]), 1)
-    # A second round in the same CTA costs less than a cluster of two (measured: about 2 against 3
-    # microseconds), and rounds are only run for keys that exist; so one CTA up to two rounds' worth
-    # of table, beyond that as few chunks as two rounds each allow, or more of them (one round each at
-    # most) while they still find processors of their own.
-    n_chunks = -(-width // (2 * cap))
-    if n_chunks > 1:
-        pairs = T * K * -(-(H // K) // 8)
-        most = min(DECODE_MAX_CLUSTER, -(-width // cap))
-        n_chunks = min(n_chunks, DECODE_MAX_CLUSTER)
-        while n_chunks < most and pairs * (n_chunks + 1) <= _sm_count(qkv.device):
-            n_chunks += 1
+    pairs = T * K * -(-(H // K) // 8)
+    sms = _sm_count(qkv.device)
+    small = 0 if pairs <= sms else (1 if pairs <= 2 * sms else 2)
+    n_chunks = 1
+    if small == 0:
+        # A second round in the same CTA costs less than a cluster of two (measured: about 2 against 3
+        # microseconds), and rounds are only run for keys that exist; so one CTA up to two rounds' worth
+        # of table, beyond that as few chunks as two rounds each allow, or more of them (one round each
+        # at most) while they still find processors of their own.
+        cap = max(lib.ab_attention_decode_round_keys(D, 0) // 64, 1)
+        n_chunks = -(-width // (2 * cap))
+        if n_chunks > 1:
+            most = min(DECODE_MAX_CLUSTER, -(-width // cap))
+            n_chunks = min(n_chunks, DECODE_MAX_CLUSTER)
+            while n_chunks < most and pairs * (n_chunks + 1) <= sms:
+                n_chunks += 1
     pages_per_cta = -(-width // n_chunks)
     _i32(ctx.tok_seq, T, "tok_seq")
     _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
     _check(lib.ab_attention_decode_rope_bf16(
         _p(qkv), qkv.shape[-1], _p(out), None, None, None, _p(k_pages), _p(v_pages), _p(table), table.shape[1],
         _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0), pages_per_cta,
-        n_chunks, 0, _p(cos), _p(sin), n_rot, pairing, fuse, _stream()), "attention_decode")
+        n_chunks, small, _p(cos), _p(sin), n_rot, pairing, fuse, _stream()), "attention_decode")
     return out
 
 
@@ -354,16 +354,9 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
     _need(page == 64 and tuple(k_pages.shape[1:]) == (K, 64, D) and k_pages.shape == v_pages.shape
           and k_pages.is_contiguous() and v_pages.is_contiguous(), "attention_mma: cache pages [n_pages,K,64,D]")
     lib = _lib("attention_mma")
-    if ctx.is_decode and not _decode_few(T, H, K, qkv.device):
-        # many (sequence, head) pairs: one warp each, no merge and no scratch
-        _i32(ctx.tok_seq, T, "tok_seq")
-        _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
-        _check(lib.ab_attention_decode_wide_bf16(
-            _p(qkv), qkv.shape[-1], _p(out), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_seq),
-            _p(ctx.kv_len), T, H, K, D, ctypes.c_float(scale), int(window or 0), _stream()), "attention_decode_wide")
-        return out
     if ctx.is_decode:
-        return _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window)
+        _i32(ctx.tok_seq, T, "tok_seq")
+        return _attention_decode(qkv, out, cache, ctx, H, K, D, scale, window)
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
     if USE_TCGEN05_ATTENTION and T >= 128 and qkv.shape[0] >= T:
@@ -394,25 +387,24 @@ def attention(qkv, out, cache, ctx, H, K, D, scale, window=0):
                           ctx.n_tokens, H, K, D, scale, window)
 
 
-FUSE_ROPE_DECODE = True          # decode steps of few sequences: rotation and append inside the attention kernel
+FUSE_ROPE_DECODE = True          # decode steps: rotation and append inside the attention kernel
 
 
 def rope_attention(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, write_cache=True):
     """Position rotation of q and k (`rot` = (cos, sin, n_rot, pairing) or None), append of k and v to
     the cache (unless `write_cache` is off: a layer that reads another layer's cache), then attention
-    of the step's tokens over the cache.  Decode steps of few sequences in bfloat16 do all of it in
-    one kernel; everything else runs the rotation kernel and then `attention`."""
+    of the step's tokens over the cache.  Decode steps in bfloat16 do all of it in one kernel; everything else runs the rotation kernel and then `attention`."""
     cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
     T = ctx.n_tokens
     if (FUSE_ROPE_DECODE and ctx.is_decode and qkv.dtype == torch.bfloat16 and D % 16 == 0 and D <= 256
-            and H // K <= 64 and n_rot % 16 == 0 and _decode_few(T, H, K, qkv.device)):
+            and H // K <= 64 and n_rot % 16 == 0):
         _cuda(qkv, out, cache.k, cache.v, cache.block_table)
         _need(out.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16 and qkv.is_contiguous()
               and out.is_contiguous() and qkv.shape[-1] == (H + 2 * K) * D and out.numel() >= T * H * D
               and H % K == 0, "rope_attention takes contiguous bfloat16 qkv [T,(H+2K)D], out [T,H*D]")
         _need(tuple(cache.k.shape[1:]) == (K, 64, D) and cache.k.shape == cache.v.shape and cache.k.is_contiguous()
               and cache.v.is_contiguous(), "rope_attention: cache pages [n_pages,K,64,D]")
-        return _attention_decode_few(qkv, out, cache, ctx, H, K, D, scale, window, rot, 2 if write_cache else 1)
+        return _attention_decode(qkv, out, cache, ctx, H, K, D, scale, window, rot, 2 if write_cache else 1)
     rope_append(qkv, cos, sin, ctx.tok_pos, ctx.tok_seq, cache.block_table, cache.k, cache.v, T, H, K, D, n_rot,
                 pairing, write_cache=write_cache)
     return attention(qkv, out, cache, ctx, H, K, D, scale, window)

@@ -214,7 +214,7 @@ def run_ours(args):
     layers_full = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
-    model = Model.random(cfg, seed=0, n_ctx=CONTEXT, dtype="bfloat16", max_batch=64)
+    model = Model.random(cfg, seed=0, n_ctx=CONTEXT, dtype="bfloat16", max_batch=max(64, args.batch or 0))
     weights = model_bytes(model)
     kv_per_token = sum(g.bytes_per_token for g in model.engine.cache.kv_groups)
 

@@ -483,3 +483,29 @@ def test_rope_attention_fused_decode(H, K, D, n_rot, pairing, window, write_cach
     assert torch.equal(o1, o2), f"outputs differ by {(o1.float() - o2.float()).abs().max().item()}"
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
     assert (o1[3].float().abs() > 0).any() and torch.equal(o1[2], torch.full_like(o1[2], 7.0))
+
+
+@pytest.mark.parametrize("H,K,D,B", [(8, 4, 64, 50), (8, 4, 64, 90), (4, 4, 128, 80), (2, 2, 256, 160), (24, 1, 64, 200)])
+def test_attention_decode_many_sequences(H, K, D, B):
+    """More (sequence, head) pairs than processors: the smaller CTAs, several rounds each; lengths
+    from one key to several rounds' worth, with a window on top."""
+    from alpacca_b200 import ops
+    from alpacca_b200.cache import KVLayerView
+    lengths = [1 + (37 * b * b + 11 * b) % 700 for b in range(B)]
+    table, kp, vp = make_paged(lengths, sum(-(-n // 64) for n in lengths) + 3, K, D, torch.bfloat16, seed=B)
+    qkv = rnd(B, (H + 2 * K) * D, dtype=torch.bfloat16, seed=17)
+    check = sorted(set([0, 1, B // 2, B - 1, max(range(B), key=lambda b: lengths[b])]))
+    ks, vs = {}, {}
+    for b, n in enumerate(lengths):
+        kk, vv = rnd(n, K, D, dtype=torch.bfloat16, seed=18 + b), rnd(n, K, D, dtype=torch.bfloat16, seed=931 + b)
+        fill_cache(table.cpu(), kp, vp, b, kk, vv)
+        if b in check:
+            ks[b], vs[b] = kk, vv
+    ctx = decode_ctx(lengths)
+    q = qkv.double().cpu().view(B, H + 2 * K, D)[:, :H]
+    for window in (0, 100):
+        out = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+        ops.attention(qkv, out, KVLayerView(kp, vp, table, None), ctx, H, K, D, D ** -0.5, window)
+        for b in check:
+            want = ref_attention(q[b:b + 1], ks[b].double().cpu(), vs[b].double().cpu(), [lengths[b] - 1], D ** -0.5, window)
+            close(out[b].view(1, H, D), want, "bfloat16", f"sequence {b} of {lengths[b]}, window {window}")
