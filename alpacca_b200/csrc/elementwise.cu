@@ -153,11 +153,77 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const T* _
   }
 }
 
+// The same for rows short enough that a thread keeps its share in registers (up to RV x 4 elements per
+// thread): the row, its delta and the norm weights are asked for at once and read once; the sum runs
+// over the same elements in the same order as in the kernel above.
+template <typename T, int RV>
+__global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, T* __restrict__ out,
+                                       const int* __restrict__ rows, int n_out, int width, float eps) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
+  const int i_out = blockIdx.x;
+  if (i_out >= n_out) return;
+  const int src = rows ? rows[i_out] : i_out;
+  float* r = residual + (size_t)src * width;
+  const T* d = delta ? delta + (size_t)src * width : nullptr;
+  const bool write_back = (d != nullptr) && (rows == nullptr);
+  float4 v[RV], w[RV];
+  Vec4<T> dv[RV];
+#pragma unroll
+  for (int j = 0; j < RV; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < width) {
+      v[j] = *reinterpret_cast<const float4*>(r + i);
+      if (d) dv[j].load(d + i);
+      if (out) w[j] = *reinterpret_cast<const float4*>(weight + i);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < RV; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < width) {
+      if (d) {
+        v[j].x += dv[j].get(0); v[j].y += dv[j].get(1); v[j].z += dv[j].get(2); v[j].w += dv[j].get(3);
+        if (write_back) *reinterpret_cast<float4*>(r + i) = v[j];
+      }
+      ss += v[j].x * v[j].x;
+      ss += v[j].y * v[j].y;
+      ss += v[j].z * v[j].z;
+      ss += v[j].w * v[j].w;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  if (out == nullptr) return;
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  T* o = out + (size_t)i_out * width;
+#pragma unroll
+  for (int j = 0; j < RV; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < width) {
+      Vec4<T> ov;
+      ov.set((v[j].x * inv) * w[j].x, (v[j].y * inv) * w[j].y, (v[j].z * inv) * w[j].z, (v[j].w * inv) * w[j].w);
+      ov.store(o + i);
+    }
+  }
+}
+
 AB_API int ab_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, int dtype,
                           const int* rows, int n_out, int width, float eps, cudaStream_t stream) {
   if (n_out <= 0) return AB_OK;
   if (width % 4 == 0) {
     const int vthreads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+    if (width <= vthreads * 4 * 4 && (dtype == AB_F32 || dtype == AB_BF16)) {
+      if (dtype == AB_F32)
+        ab_launch(add_rmsnorm_reg_kernel<float, 4>, n_out, vthreads, 0, stream, residual, (const float*)delta, weight,
+                  (float*)out, rows, n_out, width, eps);
+      else
+        ab_launch(add_rmsnorm_reg_kernel<bf16, 4>, n_out, vthreads, 0, stream, residual, (const bf16*)delta, weight,
+                  (bf16*)out, rows, n_out, width, eps);
+      return ab_launch_status();
+    }
     if (dtype == AB_F32)
       ab_launch(add_rmsnorm_vec4_kernel<float>, n_out, vthreads, 0, stream, residual, (const float*)delta, weight,
                 (float*)out, rows, n_out, width, eps);
