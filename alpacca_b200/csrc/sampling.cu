@@ -150,9 +150,23 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   // ---- maximum and its first index -------------------------------------
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
-    const float v = l[i];
-    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    // rows start on 16-byte boundaries: four logits per load, several loads in flight
+    const float4* l4 = reinterpret_cast<const float4*>(l);
+    const int n4 = vocab >> 2;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += SAMPLE_THREADS) {
+      const float4 q = l4[i];
+      const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (e[j] > bv || (e[j] == bv && 4 * i + j < bi)) { bv = e[j]; bi = 4 * i + j; }
+    }
+  } else {
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+      const float v = l[i];
+      if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
