@@ -23,6 +23,13 @@
 // K slices (grid z): every CTA parks its float32 tile in scratch memory; the CTA
 // that arrives last for a tile adds the slices in slice order and runs the tail.
 //
+// Large products (rows = tokens, one 128 x 256 tile after another) run a second, persistent form of
+// the kernel: one CTA per processor walks its share of the tiles; the accumulator is double-buffered
+// in TMEM (2 x 256 columns: all of it), so the tail of one tile (TMEM -> registers -> activation ->
+// global memory) runs under the main loop of the next, and the ring of stages never drains between
+// tiles.  Tiles that share a 256-row panel of the weights are taken by neighbouring CTAs, so the
+// panel is read from memory once and from L2 after that.
+//
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT failed tries a thread
 // records a code in `status`, and every role falls through to the common end, where
 // TMEM is given back.  The kernel cannot hang on a barrier that never completes.
@@ -60,6 +67,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (done) return true;
   }
   return false;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
@@ -349,6 +359,132 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------
+// The persistent form for rows = tokens: tiles of 128 x 256, accumulators double-buffered in TMEM.
+// ---------------------------------------------------------------------------
+#define TP_BN 256
+#define TP_STAGES 4
+#define TP_A_BYTES (TC_BM * TC_BK * 2)
+#define TP_B_BYTES (TP_BN * TC_BK * 2)
+#define TP_STAGE_BYTES (TP_A_BYTES + TP_B_BYTES)
+#define TP_SMEM (TP_STAGES * TP_STAGE_BYTES + 1024 + 256)
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                          void* __restrict__ Y, const float* __restrict__ bias, int* __restrict__ status, int M, int N,
+                          int K, int ldy, int tiles_m, int n_tiles) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + TP_STAGES * TP_STAGE_BYTES);
+  uint64_t* empty = full + TP_STAGES;
+  uint64_t* acc_full = empty + TP_STAGES;      // [2] the MMAs of a tile are done
+  uint64_t* acc_empty = acc_full + 2;          // [2] the tail has read the buffer (one arrival per tail warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TP_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // weights of the first stages before the wait (they do not depend on the kernel before)
+      int it = 0;
+      bool ok = true;
+      const int first = blockIdx.x;
+      const int early = first < n_tiles ? min(nkb, TP_STAGES) : 0;
+      const int n0_first = (first / tiles_m) * TP_BN, m0_first = (first % tiles_m) * TC_BM;
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(full + i, TP_STAGE_BYTES);
+        tma_load_2d(base + i * TP_STAGE_BYTES + TP_A_BYTES, &map_w, i * TC_BK, n0_first, full + i);
+      }
+      pdl_wait();
+      pdl_trigger();
+      for (int i = 0; i < early; ++i) tma_load_2d(base + i * TP_STAGE_BYTES, &map_x, i * TC_BK, m0_first, full + i);
+      for (int tile = first; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TP_BN;
+        for (int kb = (tile == first ? early : 0); kb < nkb; ++kb) {
+          const int i = it + kb;
+          const int s = i % TP_STAGES;
+          if (i >= TP_STAGES && !mbar_wait(empty + s, ((i / TP_STAGES) - 1) & 1)) { atomicExch(status, 11); ok = false; break; }
+          mbar_expect_tx(full + s, TP_STAGE_BYTES);
+          tma_load_2d(base + s * TP_STAGE_BYTES + TP_A_BYTES, &map_w, kb * TC_BK, n0, full + s);
+          tma_load_2d(base + s * TP_STAGE_BYTES, &map_x, kb * TC_BK, m0, full + s);
+        }
+        it += nkb;
+      }
+    } else {
+      pdl_wait();
+    }
+  } else if (warp == 1) {
+    pdl_wait();
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TP_BN >> 3) << 17) |
+                                 ((uint32_t)(TC_BM >> 4) << 24);
+      int it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+        const int buf = lt & 1;
+        if (lt >= 2 && !mbar_wait(acc_empty + buf, ((lt >> 1) - 1) & 1)) { atomicExch(status, 12); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + (uint32_t)buf * TP_BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % TP_STAGES;
+          if (!mbar_wait(full + s, (it / TP_STAGES) & 1)) { atomicExch(status, 13); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_addr(base + s * TP_STAGE_BYTES), sb = sa + TP_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)
+            umma_bf16(acc, umma_desc(sa + k * 32), umma_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty + s);
+        }
+        if (ok) umma_commit(acc_full + buf);
+      }
+    }
+  } else {
+    pdl_wait();
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+      const int buf = lt & 1;
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TP_BN;
+      ok = mbar_wait(acc_full + buf, (lt >> 1) & 1);
+      if (!ok) atomicExch(status, 14);
+      ok = __all_sync(0xffffffffu, ok);      // tcgen05.ld below is warp-wide
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = 0; c0 < TP_BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * TP_BN + c0, v);
+        tail16<EPI, false>(v, m0 + row, n0 + c0, M, N, bias, Y, ldy, lane);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + buf);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+  }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -455,6 +591,44 @@ AB_API int ab_gemm_tc(const void* X, const void* W, const float* bias, void* Y, 
     case EPI_STORE_BF16: AB_GO(EPI_STORE_BF16);
     case EPI_STORE_F32: AB_GO(EPI_STORE_F32);
     case EPI_SWIGLU_BF16: AB_GO(EPI_SWIGLU_BF16);
+  }
+#undef AB_GO
+  return AB_BAD_ARG;
+}
+
+// The persistent form: Y = X[M,K] . W[N,K]^T for many rows, tiles of 128 x 256, one CTA per processor.
+AB_API int ab_gemm_tc_persistent(const void* X, const void* W, const float* bias, void* Y, int M, int N, int K,
+                                 int ldy, int epilogue_kind, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return AB_OK;
+  if (K <= 0 || (K % 8)) return AB_BAD_ARG;
+  if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  int* status = status_word();
+  if (!status) return AB_BAD_ARG;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, X, M, K, TC_BM)) return AB_BAD_ARG;
+  if (!make_map(&mw, W, N, K, TP_BN)) return AB_BAD_ARG;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + TP_BN - 1) / TP_BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int grid = n_tiles < sms ? n_tiles : sms;
+#define AB_GO(E)                                                                                                   \
+  {                                                                                                                \
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM); \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
+    e = ab_launch(gemm_tc_persistent_kernel<E>, dim3(grid), dim3(TC_THREADS), (size_t)TP_SMEM, stream, mx, mw, Y,  \
+                  bias, status, M, N, K, ldy, tiles_m, n_tiles);                                                   \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
+    return ab_launch_status();                                                                                     \
+  }
+  switch (epilogue_kind) {
+    case EPI_STORE_BF16: AB_GO(EPI_STORE_BF16)
+    case EPI_STORE_F32: AB_GO(EPI_STORE_F32)
+    case EPI_SWIGLU_BF16: AB_GO(EPI_SWIGLU_BF16)
   }
 #undef AB_GO
   return AB_BAD_ARG;

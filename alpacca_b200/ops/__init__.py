@@ -214,6 +214,9 @@ GEMV_MAX_ROWS = 8           # up to here the skinny-matrix kernel is the fastest
 GEMV_NARROW_MAX_ROWS = 16   # ... and up to here for matrices of no more 16-row slabs than the GPU has SMs
 #                             (2048x2048: 4.1 against 5.3 us for the library, 2048x8192: 12.2 against 13.2)
 TC_SWAP_MAX_ROWS = 64       # up to here the tcgen05 kernel with the weights on the 128-row side
+TC_PERSISTENT_MIN_ROWS = 1024   # from here the persistent tcgen05 product with the SwiGLU tail beats the library
+#                                 product followed by the activation kernel (16384x2048: 57.9 against 57.8 us at
+#                                 1,024 rows, 100 against 120 at 2,048, 190 against 235 at 4,096)
 _SM_COUNT: dict = {}
 
 
@@ -493,13 +496,15 @@ def decode_advance(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, 
         int(window), _p(history), _p(counter), hist_len, n_rows, _stream()), "decode_advance")
 
 
-def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None, slices=None):
+def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None, slices=None, persistent=True):
     """out[:n] = x[:n] @ w^T (+ bias) on the tcgen05 tensor cores (TMA-fed, TMEM accumulators).
 
     x [M,K], w [N,K] bfloat16; out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row
     interleaved gate|up matrix and out is bfloat16 [M, N/2].  `swap` puts the weights on the
     128-row side of the MMA (the batch, up to 256 rows, becomes the columns): the shape for decode
-    steps.  `bn` is the MMA's column count per tile, `slices` the number of K slices.
+    steps.  `bn` is the MMA's column count per tile, `slices` the number of K slices.  Without `swap`,
+    256-wide tiles and one slice run as the persistent kernel (one CTA per SM walks the tiles) unless
+    `persistent` is off.
     """
     _cuda(x, w, out, bias)
     n = x.shape[0] if n_rows is None else n_rows
@@ -523,6 +528,11 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
         epi = 1 if out.dtype == torch.float32 else 0
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemm_tc: bias f32 [N]")
+    if not swap and bn == 256 and slices in (None, 1) and persistent:
+        # many rows: the persistent form (tails under the next tile's main loop)
+        _check(_lib("gemm_tc").ab_gemm_tc_persistent(_p(x), _p(w), _p(bias), _p(out), n, N, K, out.shape[-1], epi,
+                                                     _stream()), "gemm_tc")
+        return out
     rows_a, rows_b = (N, n) if swap else (n, N)
     tiles = -(-rows_a // 128) * -(-rows_b // bn)
     if slices is None:

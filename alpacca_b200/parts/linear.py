@@ -79,4 +79,7 @@ class Linear(Part):
                 return ops.gemv_bf16(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True)
             if n <= ops.TC_SWAP_MAX_ROWS:
                 return ops.gemm_tc(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, swap=True, slices=1)
+            if n >= ops.TC_PERSISTENT_MIN_ROWS:
+                # long prompts: the persistent tcgen05 product with the activation in its tail
+                return ops.gemm_tc(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, swap=False)
         return ops.swiglu(self.forward(x, n_rows=n), act, n_rows=n)

@@ -509,3 +509,33 @@ def test_attention_decode_many_sequences(H, K, D, B):
         for b in check:
             want = ref_attention(q[b:b + 1], ks[b].double().cpu(), vs[b].double().cpu(), [lengths[b] - 1], D ** -0.5, window)
             close(out[b].view(1, H, D), want, "bfloat16", f"sequence {b} of {lengths[b]}, window {window}")
+
+
+@pytest.mark.parametrize("M,N,K", [(2500, 2100, 328), (4000, 3000, 200), (130, 300, 4104)])
+def test_gemm_tc_persistent(M, N, K):
+    """The persistent form of the tcgen05 product: more tiles than processors (a CTA walks several,
+    both accumulator buffers in turn), ragged edges in every direction, both output types."""
+    from alpacca_b200 import ops
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.1), rnd(N, seed=3)
+    want = x.double() @ w.double().T + bias.double()
+    for dt, tol in ((torch.float32, "float32"), (torch.bfloat16, "bfloat16")):
+        out = torch.full((M, N), 9.0, dtype=dt, device="cuda")
+        ops.gemm_tc(x, w, out, bias=bias, swap=False, bn=256, slices=1)
+        close(out, want, tol, f"persistent gemm_tc {dt}")
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(3000, 1304, 264), (1024, 512, 2048)])
+def test_gemm_tc_persistent_swiglu(M, F, K):
+    from alpacca_b200 import ops
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    gate, up = rnd(F, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5), rnd(F, K, dtype=torch.bfloat16, seed=3, scale=K ** -0.5)
+    bg, bu = rnd(F, seed=4), rnd(F, seed=5)
+    w = torch.cat([gate.view(F // 8, 8, K), up.view(F // 8, 8, K)], dim=1).reshape(2 * F, K).contiguous()
+    bias = torch.cat([bg.view(F // 8, 8), bu.view(F // 8, 8)], dim=1).reshape(2 * F).contiguous()
+    g = x.double() @ gate.double().T + bg.double()
+    u = x.double() @ up.double().T + bu.double()
+    out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tc(x, w, out, bias=bias, swiglu=True, swap=False)
+    close(out, g / (1 + torch.exp(-g)) * u, "bfloat16", "persistent swiglu epilogue")
+    assert ops.gemm_tc_status() == 0
