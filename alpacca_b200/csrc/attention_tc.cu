@@ -9,14 +9,19 @@
 // page of the cache, 64 keys of one KV head, is one TMA box).  For tile j:
 //
 //   MMA warp      S_j = Q K_j^T           (M 128, N 64, K = head size)   -> TMEM
-//   softmax warps read S_j from TMEM (a row per thread), scale, mask, running max
+//   softmax warps read S_j from TMEM (a row per thread), scale, mask, maximum
 //                 and sum, P_j = 2^(s - m) in bfloat16 -> shared memory (the layout
 //                 the MMA reads: 128-byte rows, swizzled)
-//   MMA warp      T_j = P_j V_j           (M 128, N head size, K 64)     -> TMEM
-//   softmax warps O = O * 2^(m_old - m_new) + T_j   in registers
+//   MMA warp      O += P_j V_j            (M 128, N head size, K 64)     -> TMEM
 //
-// S and T are double-buffered in TMEM and P in shared memory, so the MMAs of tile
-// j+1 run while tile j's softmax does; two CTAs share an SM.  Scores are
+// The output accumulates in TMEM over all tiles and comes to registers once, at
+// the end.  m is the reference the exponentials of a row are taken against; it
+// follows the row's running maximum lazily: only when the maximum has outgrown it
+// by more than 2^8 is m moved and the row of O (and the running sum) rescaled by
+// 2^(m_old - m_new), a read-modify-write of TMEM that the softmax threads do
+// between two products.  Until then P is at most 2^8, well inside bfloat16 and
+// float32.  S is double-buffered in TMEM and P in shared memory, so the MMAs of
+// tile j+1 run while tile j's softmax does; two CTAs share an SM.  Scores are
 // (q.k) * scale, key s visible to position p iff lo <= s <= p
 // (alpacca/model.py:457-467).
 //
@@ -94,6 +99,18 @@ __device__ __forceinline__ void at_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void at_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void at_st16(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+__device__ __forceinline__ void at_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+#define AT_LAZY 8.0f     // a row's reference follows its maximum when that is more than 2^8 ahead
 __device__ __forceinline__ float at_exp2(float x) {      // 2^x, the hardware approximation (2^-inf = 0)
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -127,8 +144,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t* kv_empty = kv_full + AT_STAGES;      // STAGES
   uint64_t* s_full = kv_empty + AT_STAGES;       // 2
   uint64_t* p_full = s_full + 2;                 // 2
-  uint64_t* o_full = p_full + 2;                 // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint64_t* o_done = p_full + 2;                 // 1: completes once per product O += P_j V_j
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = H / K;
@@ -142,7 +159,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   if (threadIdx.x == 0) {
     at_bar_init(q_full, 1);
     for (int s = 0; s < AT_STAGES; ++s) { at_bar_init(kv_full + s, 1); at_bar_init(kv_empty + s, 1); }
-    for (int i = 0; i < 2; ++i) { at_bar_init(s_full + i, 1); at_bar_init(p_full + i, 128); at_bar_init(o_full + i, 1); }
+    for (int i = 0; i < 2; ++i) { at_bar_init(s_full + i, 1); at_bar_init(p_full + i, 128); }
+    at_bar_init(o_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -153,7 +171,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns: S tiles at 0 and 64, T tiles at 128 and 192
+  // TMEM columns: S tiles at 0 and 64, O at 128
   pdl_wait();
   pdl_trigger();
 
@@ -209,8 +227,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t p_addr = at_smem(base + AtSmem::P_OFF + (j & 1) * AtSmem::P_BYTES);
 #pragma unroll
         for (int k = 0; k < AT_KEYS / 16; ++k)     // 16 keys per MMA: 32 bytes along P's rows, 2 groups of 8 V rows
-          at_mma(tmem + 128 + (j & 1) * 64, at_desc(p_addr + k * 32), at_desc(v_addr + k * 2048), idesc_t, k > 0 ? 1u : 0u);
-        at_commit(o_full + (j & 1));
+          at_mma(tmem + 128, at_desc(p_addr + k * 32), at_desc(v_addr + k * 2048), idesc_t, (j > 0 || k > 0) ? 1u : 0u);
+        at_commit(o_done);
         at_commit(kv_empty + s);                   // K and V of this stage are read when these MMAs are done
       }
     }
@@ -226,28 +244,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       pos = tok_pos[q0 + r / G];
       lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     }
-    float o[AT_D];
-#pragma unroll
-    for (int d = 0; d < AT_D; ++d) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    float m_ref = -INFINITY, l_run = 0.f;       // the row's reference and its sum of 2^(s - m_ref)
     bool ok = true;
     unsigned char* p_rows = base + AtSmem::P_OFF + (size_t)r * 128;
-
-    auto accumulate = [&](int j, float corr) {        // O = O * corr + T_j
-      if (!at_wait(o_full + (j & 1), (j >> 1) & 1)) { atomicExch(status, 15); ok = false; }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) return;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c0 = 0; c0 < AT_D; c0 += 32) {        // two loads in flight, then their 32 multiply-adds
-        float t[32];
-        at_ld16(tmem + lane_base + 128 + (j & 1) * 64 + c0, t);
-        at_ld16(tmem + lane_base + 128 + (j & 1) * 64 + c0 + 16, t + 16);
-        at_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) o[c0 + c] = fmaf(o[c0 + c], corr, t[c]);
-      }
-    };
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       if (!at_wait(s_full + (j & 1), (j >> 1) & 1)) { atomicExch(status, 16); ok = false; }
@@ -276,10 +275,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mx4[2] = fmaxf(mx4[2], sc[c + 2]);
         mx4[3] = fmaxf(mx4[3], sc[c + 3]);
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_new = fmaxf(m_run, mx * scale_log2);
-      const float sub = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = at_exp2(m_run - sub);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      // move the reference only when the maximum has outgrown it by a lot (or there was none yet)
+      const bool move = (mx > m_ref + AT_LAZY) || (m_ref == -INFINITY && mx > -INFINITY);
+      float corr = 1.f;
+      if (move) {
+        corr = (m_ref == -INFINITY) ? 0.f : at_exp2(m_ref - mx);
+        m_ref = mx;
+        l_run *= corr;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, move)) {
+        // rescale this warp's rows of O in TMEM, after the product before this tile has landed there
+        if (!at_wait(o_done, (j - 1) & 1)) { atomicExch(status, 15); ok = false; }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int c0 = 0; c0 < AT_D; c0 += 32) {
+          float t[32];
+          at_ld16(tmem + lane_base + 128 + c0, t);
+          at_ld16(tmem + lane_base + 128 + c0 + 16, t + 16);
+          at_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) t[c] *= corr;
+          at_st16(tmem + lane_base + 128 + c0, t);
+          at_st16(tmem + lane_base + 128 + c0 + 16, t + 16);
+        }
+        at_st_wait();
+      }
+      const float sub = (m_ref == -INFINITY) ? 0.f : m_ref;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[AT_KEYS / 2];
 #pragma unroll
@@ -291,13 +315,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pa);
         packed[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&pb);
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      m_run = m_new;
-      l_run = l_run * corr + sum;
-      // the previous tile's product uses the P buffer of two tiles ago and must be added before O is rescaled again
-      if (j > 0) accumulate(j - 1, corr_prev);
-      if (!ok) break;
-      corr_prev = corr;
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // P row: 8 pieces of 16 bytes, piece c at place c ^ (row % 8) (the 128-byte swizzle)
       unsigned char* prow = p_rows + (size_t)(j & 1) * AtSmem::P_BYTES;
 #pragma unroll
@@ -308,19 +326,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       at_arrive(p_full + (j & 1));
     }
-    if (ok && n_tiles > 0) accumulate(n_tiles - 1, corr_prev);
-    if (ok && row_ok) {
+    if (ok && n_tiles > 0) {
+      if (!at_wait(o_done, (n_tiles - 1) & 1)) { atomicExch(status, 17); ok = false; }
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* dst = out + ((size_t)(q0 + r / G) * H + kh * G + r % G) * AT_D;
 #pragma unroll
-      for (int c = 0; c < AT_D; c += 8) {
-        uint32_t w[4];
+      for (int c0 = 0; c0 < AT_D; c0 += 32) {
+        float t[32];
+        if (n_tiles > 0) {
+          at_ld16(tmem + lane_base + 128 + c0, t);
+          at_ld16(tmem + lane_base + 128 + c0 + 16, t + 16);
+          at_ld_wait();
+        } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          __nv_bfloat162 pr = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
-          w[e] = *reinterpret_cast<uint32_t*>(&pr);
+          for (int c = 0; c < 32; ++c) t[c] = 0.f;
         }
-        *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (row_ok) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 pr = __floats2bfloat162_rn(t[c + 2 * e] * inv, t[c + 2 * e + 1] * inv);
+              w[e] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+            *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
       }
     }
   }
