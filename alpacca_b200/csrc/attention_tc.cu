@@ -10,9 +10,10 @@
 //
 //   MMA warp      S_j = Q K_j^T           (M 128, N 64, K = head size)   -> TMEM
 //   softmax warps read S_j from TMEM (a row per thread), scale, mask, maximum
-//                 and sum, P_j = 2^(s - m) in bfloat16 -> shared memory (the layout
-//                 the MMA reads: 128-byte rows, swizzled)
-//   MMA warp      O += P_j V_j            (M 128, N head size, K 64)     -> TMEM
+//                 and sum, P_j = 2^(s - m) in bfloat16 -> TMEM (a row per lane, two
+//                 keys per 32-bit column: the layout of an MMA's first operand there)
+//   MMA warp      O += P_j V_j            (M 128, N head size, K 64; P read from TMEM,
+//                 V from shared memory)                                  -> TMEM
 //
 // The output accumulates in TMEM over all tiles and comes to registers once, at
 // the end.  m is the reference the exponentials of a row are taken against; it
@@ -20,7 +21,7 @@
 // by more than 2^8 is m moved and the row of O (and the running sum) rescaled by
 // 2^(m_old - m_new), a read-modify-write of TMEM that the softmax threads do
 // between two products.  Until then P is at most 2^8, well inside bfloat16 and
-// float32.  S is double-buffered in TMEM and P in shared memory, so the MMAs of
+// float32.  S and P are double-buffered in TMEM, so the MMAs of
 // tile j+1 run while tile j's softmax does; two CTAs share an SM.  Scores are
 // (q.k) * scale, key s visible to position p iff lo <= s <= p
 // (alpacca/model.py:457-467).
@@ -34,7 +35,7 @@
 #define AT_ROWS 128
 #define AT_KEYS 64
 #define AT_D 64
-#define AT_STAGES 3      // 96 KB of shared memory per CTA, so that two CTAs fit an SM
+#define AT_STAGES 4      // 80 KB of shared memory per CTA; two CTAs fit an SM (TMEM: 256 columns each)
 #define AT_THREADS 192
 #define AT_SPIN (1u << 20)
 #define AT_LOG2E 1.4426950408889634f
@@ -85,6 +86,14 @@ __device__ __forceinline__ void at_mma(uint32_t tmem_d, uint64_t da, uint64_t db
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the first operand in TMEM (P: a row per lane, two bfloat16 per column)
+__device__ __forceinline__ void at_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void at_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(bar)) : "memory");
 }
@@ -109,6 +118,13 @@ __device__ __forceinline__ void at_st16(uint32_t taddr, const float* v) {
         "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
       : "memory");
 }
+__device__ __forceinline__ void at_st16u(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void at_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 #define AT_LAZY 8.0f     // a row's reference follows its maximum when that is more than 2^8 ahead
 __device__ __forceinline__ float at_exp2(float x) {      // 2^x, the hardware approximation (2^-inf = 0)
@@ -121,11 +137,9 @@ struct AtSmem {
   // all tiles are [rows][64] bfloat16 = 128-byte rows, 1024-byte aligned
   static constexpr int Q_BYTES = AT_ROWS * 128;
   static constexpr int KV_BYTES = AT_KEYS * 128;          // one K or V tile
-  static constexpr int P_BYTES = AT_ROWS * 128;
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = Q_OFF + Q_BYTES;                               // [STAGES][K | V]
-  static constexpr int P_OFF = KV_OFF + AT_STAGES * 2 * KV_BYTES;              // [2]
-  static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;
+  static constexpr int BAR_OFF = KV_OFF + AT_STAGES * 2 * KV_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -171,7 +185,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns: S tiles at 0 and 64, O at 128
+  // TMEM columns: S tiles at 0 and 64, O at 128, P tiles (32 columns each) at 192 and 224
   pdl_wait();
   pdl_trigger();
 
@@ -224,10 +238,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int s = j % AT_STAGES;
         const uint32_t v_addr = at_smem(base + AtSmem::KV_OFF + s * 2 * AtSmem::KV_BYTES + AtSmem::KV_BYTES);
-        const uint32_t p_addr = at_smem(base + AtSmem::P_OFF + (j & 1) * AtSmem::P_BYTES);
 #pragma unroll
-        for (int k = 0; k < AT_KEYS / 16; ++k)     // 16 keys per MMA: 32 bytes along P's rows, 2 groups of 8 V rows
-          at_mma(tmem + 128, at_desc(p_addr + k * 32), at_desc(v_addr + k * 2048), idesc_t, (j > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < AT_KEYS / 16; ++k)     // 16 keys per MMA: 8 columns of P, 2 groups of 8 V rows
+          at_mma_ts(tmem + 128, tmem + 192 + (j & 1) * 32 + k * 8, at_desc(v_addr + k * 2048), idesc_t,
+                    (j > 0 || k > 0) ? 1u : 0u);
         at_commit(o_done);
         at_commit(kv_empty + s);                   // K and V of this stage are read when these MMAs are done
       }
@@ -246,7 +260,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     float m_ref = -INFINITY, l_run = 0.f;       // the row's reference and its sum of 2^(s - m_ref)
     bool ok = true;
-    unsigned char* p_rows = base + AtSmem::P_OFF + (size_t)r * 128;
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       if (!at_wait(s_full + (j & 1), (j >> 1) & 1)) { atomicExch(status, 16); ok = false; }
@@ -316,13 +329,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         packed[(c >> 1) + 1] = *reinterpret_cast<uint32_t*>(&pb);
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // P row: 8 pieces of 16 bytes, piece c at place c ^ (row % 8) (the 128-byte swizzle)
-      unsigned char* prow = p_rows + (size_t)(j & 1) * AtSmem::P_BYTES;
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
-            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the tensor cores' reads
+      // P row: 32 columns of this thread's lane (two keys each)
+      at_st16u(tmem + lane_base + 192 + (j & 1) * 32, packed);
+      at_st16u(tmem + lane_base + 192 + (j & 1) * 32 + 16, packed + 16);
+      at_st_wait();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       at_arrive(p_full + (j & 1));
     }
