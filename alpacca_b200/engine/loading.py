@@ -9,7 +9,6 @@ import torch
 from ..config import ModelConfig, config_from_dict, get_architecture, load_config
 from ..parts.base import BuildOptions
 from ..weights import FolderSource, RandomSource, write_safetensors
-from ..weights.sources import DTYPE_NAMES
 from .model import DecoderModel
 
 DTYPE_BY_NAME = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,

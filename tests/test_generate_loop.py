@@ -1,5 +1,4 @@
 """The generation loop's decisions, with stand-ins for the engine and the sampler (CPU)."""
-import numpy as np
 import pytest
 import torch
 

@@ -3,7 +3,6 @@ whole requests, the last 32 tokens one by one, unequal batches one after another
 with slots used again, long decoding, the first tokens of a sequence."""
 import numpy as np
 import pytest
-import torch
 
 import tiny
 from helpers import CONFIGS, check_logits, plain_logits

@@ -3,7 +3,6 @@ at sizes other than the engine's: widths and vocabularies that are no power of t
 head sizes in steps of 16, several heads-per-group ratios."""
 import math
 
-import numpy as np
 import pytest
 import torch
 

@@ -1,7 +1,6 @@
 """Another architecture, defined here and nowhere in the package: a mixer with a state of fixed size
 per sequence, a layer that runs twice, a run that reads another run's cache.  It is registered, built,
 given random weights, stepped and generated from without a change to the package's files."""
-import json
 from dataclasses import dataclass
 
 import numpy as np

@@ -23,7 +23,7 @@ TOY = {"architectures": [NAME], "width": 48, "heads": 3, "kv_heads": 3, "head_di
 def define_toy():
     from alpacca_b200.config import ModelConfig, register_architecture, unregister_architecture
     from alpacca_b200.engine.model import DecoderSpec
-    from alpacca_b200.parts import (Attention, FeedForward, Linear, Norm, Part, PositionEncoding, PreNormBlock, RMSNorm,
+    from alpacca_b200.parts import (Attention, FeedForward, Norm, Part, PositionEncoding, PreNormBlock, RMSNorm,
                                     SwiGLU, TokenEmbedding, VocabHead)
     from alpacca_b200.weights import ParamSpec
 
