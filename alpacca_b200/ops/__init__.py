@@ -10,6 +10,7 @@ bad pointer or size would fault the device rather than raise.
 from __future__ import annotations
 
 import ctypes
+import math
 
 import torch
 
@@ -303,6 +304,38 @@ def _arrival_counters(device, n: int):
     return buf
 
 
+_DECODE_PLANS: dict = {}
+
+
+def _decode_attention_plan(pairs: int, width: int, D: int, sms: int):
+    """CTA size (`small` 0, 1, 2: the CTA halved that many times, 1, 2, 4 CTAs per SM) and the number of
+    chunks per sequence for the decode attention of `pairs` (sequence, KV head, head tile) triples over
+    block tables `width` pages wide: the pair with the least estimated time.  The estimate is
+    waves x (launch + rounds x round) + cluster, in microseconds, with constants measured on a B200
+    (batch 8 and 1 at contexts of 512 to 3,800 tokens, batch 32 to 256 at 512): a CTA's launch and merge
+    1.5, a round of loads and products 2.2 / 2.2 / 2.4 for the three sizes, the cluster's launch and merge
+    3.2 (a second round in the same CTA costs less than a cluster of two; rounds only run for keys
+    that exist, which the estimate cannot know: ties go to fewer chunks and larger CTAs)."""
+    key = (pairs, width, D, sms)
+    plan = _DECODE_PLANS.get(key)
+    if plan is None:
+        lib = _lib("attention_mma")
+        best = None
+        for small in (0, 1, 2):
+            cap = lib.ab_attention_decode_round_keys(D, small) / 64.0        # pages per round
+            slots = sms << small
+            for n in range(1, DECODE_MAX_CLUSTER + 1):
+                if n > 1 and n > width:
+                    break
+                rounds = math.ceil(-(-width // n) / cap)
+                waves = -(-pairs * n // slots)
+                est = waves * (1.5 + rounds * (2.2, 2.2, 2.4)[small]) + (3.2 if n > 1 else 0.0)
+                if best is None or est < best[0] - 1e-9:
+                    best = (est, small, n)
+        plan = _DECODE_PLANS[key] = (best[1], best[2])
+    return plan
+
+
 def _attention_decode(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fuse=0):
     """Decode attention: a CTA per (sequence, KV head, chunk of pages).  With few (sequence, head)
     pairs a CTA is large and a long table is cut into 2 to 8 chunks that are merged inside a
@@ -319,22 +352,7 @@ def _attention_decode(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fu
               and sin.is_contiguous() and cos.shape == sin.shape and cos.shape[-1] == n_rot // 2 and n_rot % 16 == 0
               and n_rot <= D, "rope tables must be float32 [P, n_rot/2], n_rot a multiple of 16")
     width = max(int(table.shape[1]), 1)
-    pairs = T * K * -(-(H // K) // 8)
-    sms = _sm_count(qkv.device)
-    small = 0 if pairs <= sms else (1 if pairs <= 2 * sms else 2)
-    n_chunks = 1
-    if small == 0:
-        # A second round in the same CTA costs less than a cluster of two (measured: about 2 against 3
-        # microseconds), and rounds are only run for keys that exist; so one CTA up to two rounds' worth
-        # of table, beyond that as few chunks as two rounds each allow, or more of them (one round each
-        # at most) while they still find processors of their own.
-        cap = max(lib.ab_attention_decode_round_keys(D, 0) // 64, 1)
-        n_chunks = -(-width // (2 * cap))
-        if n_chunks > 1:
-            most = min(DECODE_MAX_CLUSTER, -(-width // cap))
-            n_chunks = min(n_chunks, DECODE_MAX_CLUSTER)
-            while n_chunks < most and pairs * (n_chunks + 1) <= sms:
-                n_chunks += 1
+    small, n_chunks = _decode_attention_plan(T * K * -(-(H // K) // 8), width, D, _sm_count(qkv.device))
     pages_per_cta = -(-width // n_chunks)
     _i32(ctx.tok_seq, T, "tok_seq")
     _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
