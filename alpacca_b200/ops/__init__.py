@@ -228,11 +228,13 @@ def _sm_count(device) -> int:
     return n
 
 
-def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None):
+def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None, start_early=True):
     """out[:n] = x[:n] @ w^T (+ bias) for n <= 32 rows, bfloat16 x [M,K], w [N,K].
 
     out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row interleaved gate|up
-    matrix [2F,K] and out is bfloat16 [M,F] = silu(gate) * up.
+    matrix [2F,K] and out is bfloat16 [M,F] = silu(gate) * up.  `start_early` off: the kernel is
+    launched without programmatic dependent launch, i.e. after the kernel before it has ended (for
+    the product that follows the decode attention, see csrc/launch.cuh).
     """
     _cuda(x, w, out, bias)
     n = x.shape[0] if n_rows is None else n_rows
@@ -260,8 +262,14 @@ def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None):
         partials = torch.empty(slabs * slices * 128 * (1 if n <= 8 else 2 if n <= 16 else 4), dtype=torch.float32,
                                device=x.device)
         arrivals = _arrival_counters(x.device, slabs)
-    _check(lib.ab_gemv_bf16(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K, out.shape[-1],
-                            epi, slices, _stream()), "gemv_bf16")
+    if not start_early:
+        lib.ab_pdl_hold(1)
+    try:
+        _check(lib.ab_gemv_bf16(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K, out.shape[-1],
+                                epi, slices, _stream()), "gemv_bf16")
+    finally:
+        if not start_early:
+            lib.ab_pdl_hold(0)
     return out
 
 
@@ -433,7 +441,7 @@ def rope_attention(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, wri
     return attention(qkv, out, cache, ctx, H, K, D, scale, window)
 
 
-def linear_bf16(x, w, out, n_rows=None, bias=None):
+def linear_bf16(x, w, out, n_rows=None, bias=None, start_early=True):
     """out[:n] = x[:n] @ w^T (+ bias) for bfloat16 x [M,K], w [N,K]; out bfloat16 or float32 [M,N].
 
     Up to GEMV_MAX_ROWS rows (decode steps; GEMV_NARROW_MAX_ROWS for narrow matrices): the
@@ -446,7 +454,7 @@ def linear_bf16(x, w, out, n_rows=None, bias=None):
           "linear_bf16: x [M,K], w [N,K], out [M,N]")
     if x.shape[1] % 8 == 0 and (n <= GEMV_MAX_ROWS or (n <= GEMV_NARROW_MAX_ROWS
                                                        and -(-w.shape[0] // 16) <= _sm_count(x.device))):
-        return gemv_bf16(x, w, out, bias=bias, n_rows=n)
+        return gemv_bf16(x, w, out, bias=bias, n_rows=n, start_early=start_early)
     if n <= TC_SWAP_MAX_ROWS and out.dtype == torch.float32 and x.shape[1] % 8 == 0:
         return gemm_tc(x, w, out, bias=bias, n_rows=n, swap=True, slices=1)      # the vocabulary head
     if out.dtype == torch.float32:

@@ -44,4 +44,6 @@ class Attention(Mixer):
         att = torch.empty((h.shape[0], self.H * self.D), dtype=h.dtype, device=h.device)
         ops.rope_attention(qkv, att, cache, ctx, self.H, self.K, self.D, self.scale, self.window or 0, rot,
                            write_cache=write_cache)
-        return self.out.forward(att, n_rows=T)
+        # the attention kernel fills the SMs' shared memory, the product wants it as L1: it starts
+        # when the attention has ended, not while it runs
+        return self.out.forward(att, n_rows=T, start_early=False)

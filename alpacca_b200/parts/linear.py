@@ -62,13 +62,15 @@ class Linear(Part):
         """Uses an existing tensor as the matrix (a tied head)."""
         self.weight = tensor
 
-    def forward(self, x: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, n_rows: int | None = None, start_early: bool = True) -> torch.Tensor:
+        """`start_early` off: the product's kernel may not start before the kernel before it has ended
+        (see `ops.gemv_bf16`)."""
         n = x.shape[0] if n_rows is None else n_rows
         out = torch.empty((x.shape[0], self.out_features), dtype=self.out_dtype, device=x.device)
         if x.dtype == torch.float32:
             ops.gemm_f32(x, self.weight, out, bias=self.bias, n_rows=n)
             return out
-        return ops.linear_bf16(x, self.weight, out, n_rows=n, bias=self.bias)
+        return ops.linear_bf16(x, self.weight, out, n_rows=n, bias=self.bias, start_early=start_early)
 
     def forward_swiglu(self, x: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
         """silu(gate) * up of the interleaved gate|up product, [M, out_features / 2]."""
