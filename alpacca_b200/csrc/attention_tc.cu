@@ -1,5 +1,5 @@
 // Causal grouped-query attention for prefill on the fifth-generation tensor cores
-// (bfloat16, head size 64): scores and the per-tile output products are tcgen05
+// (bfloat16, head size 64 or 128): scores and the per-tile output products are tcgen05
 // MMAs with accumulators in tensor memory (TMEM), operands brought in by TMA with the
 // 128-byte swizzle, softmax in float32 by one thread per query row.
 //
@@ -34,8 +34,17 @@
 
 #define AT_ROWS 128
 #define AT_KEYS 64
-#define AT_D 64
-#define AT_STAGES 4      // 80 KB of shared memory per CTA; two CTAs fit an SM (TMEM: 256 columns each)
+// Head size HD is 64 or 128.  A row of 64 elements (128 bytes, the width of the swizzle) is one row of a
+// "panel"; an operand with 128 elements per row is two panels one after the other (Q: 16 KB each, a K
+// or V tile: 8 KB each).  Two CTAs share an SM: 256 TMEM columns each (HD 64: S twice, O, P twice; HD
+// 128: S twice with P over the first half of each, O 128 columns) and at most 113 KB of shared memory
+// (HD 64: Q and four stages of K and V, 80 KB; HD 128: Q and two stages, 96 KB).
+template <int HD> struct AtShape {
+  static constexpr int PANELS = HD / 64;
+  static constexpr int STAGES = HD == 64 ? 4 : 2;
+  static constexpr uint32_t O_COL = 128;
+  __host__ __device__ static constexpr uint32_t p_col(int j) { return HD == 64 ? 192u + (j & 1) * 32u : (j & 1) * 64u; }
+};
 #define AT_THREADS 192
 #define AT_SPIN (1u << 20)
 #define AT_LOG2E 1.4426950408889634f
@@ -78,6 +87,10 @@ __device__ __forceinline__ void at_tma_3d(void* dst, const CUtensorMap* map, int
 // an MN-major one (rows = k index, the 128 bytes run along n); which it is says the instruction.
 __device__ __forceinline__ uint64_t at_desc(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// an MN-major operand wider than one panel: `panel_bytes` from one 64-column panel to the next
+__device__ __forceinline__ uint64_t at_desc_mn(uint32_t saddr, uint32_t panel_bytes) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(panel_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 __device__ __forceinline__ void at_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -133,16 +146,19 @@ __device__ __forceinline__ float at_exp2(float x) {      // 2^x, the hardware ap
   return y;
 }
 
-struct AtSmem {
-  // all tiles are [rows][64] bfloat16 = 128-byte rows, 1024-byte aligned
-  static constexpr int Q_BYTES = AT_ROWS * 128;
-  static constexpr int KV_BYTES = AT_KEYS * 128;          // one K or V tile
+template <int HD> struct AtSmem {
+  // all tiles are panels of [rows][64] bfloat16 = 128-byte rows, 1024-byte aligned
+  static constexpr int Q_PANEL = AT_ROWS * 128;
+  static constexpr int KV_PANEL = AT_KEYS * 128;
+  static constexpr int Q_BYTES = AtShape<HD>::PANELS * Q_PANEL;
+  static constexpr int KV_BYTES = AtShape<HD>::PANELS * KV_PANEL;      // one K or V tile
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = Q_OFF + Q_BYTES;                               // [STAGES][K | V]
-  static constexpr int BAR_OFF = KV_OFF + AT_STAGES * 2 * KV_BYTES;
+  static constexpr int BAR_OFF = KV_OFF + AtShape<HD>::STAGES * 2 * KV_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
+template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
@@ -152,7 +168,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             int tokens_per_tile, int* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base + AtSmem::BAR_OFF);
+  using Sm = AtSmem<HD>;
+  using Sh = AtShape<HD>;
+  constexpr int AT_STAGES = Sh::STAGES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + Sm::BAR_OFF);
   uint64_t* q_full = bars;                       // 1
   uint64_t* kv_full = bars + 1;                  // STAGES
   uint64_t* kv_empty = kv_full + AT_STAGES;      // STAGES
@@ -185,7 +204,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns: S tiles at 0 and 64, O at 128, P tiles (32 columns each) at 192 and 224
+  // TMEM columns: S tiles at 0 and 64, O from 128; P tiles (32 columns each) at 192 and 224 (HD 64)
+  // or over the first half of their S tile (HD 128)
   pdl_wait();
   pdl_trigger();
 
@@ -197,16 +217,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (warp == 0) {
     if (lane == 0) {
-      at_expect_tx(q_full, AtSmem::Q_BYTES);
-      at_tma_3d(base + AtSmem::Q_OFF, &map_q, 0, kh * G, q0, q_full);
+      at_expect_tx(q_full, Sm::Q_BYTES);
+      for (int p = 0; p < Sh::PANELS; ++p)
+        at_tma_3d(base + Sm::Q_OFF + p * Sm::Q_PANEL, &map_q, p * 64, kh * G, q0, q_full);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % AT_STAGES;
         if (j >= AT_STAGES && !at_wait(kv_empty + s, ((j / AT_STAGES) - 1) & 1)) { atomicExch(status, 11); break; }
         const int row = (bt[kb_begin + j] * K + kh) * AT_KEYS;
-        unsigned char* dst = base + AtSmem::KV_OFF + s * 2 * AtSmem::KV_BYTES;
-        at_expect_tx(kv_full + s, 2 * AtSmem::KV_BYTES);
-        at_tma_2d(dst, &map_k, 0, row, kv_full + s);
-        at_tma_2d(dst + AtSmem::KV_BYTES, &map_v, 0, row, kv_full + s);
+        unsigned char* dst = base + Sm::KV_OFF + s * 2 * Sm::KV_BYTES;
+        at_expect_tx(kv_full + s, 2 * Sm::KV_BYTES);
+        for (int p = 0; p < Sh::PANELS; ++p) {
+          at_tma_2d(dst + p * Sm::KV_PANEL, &map_k, p * 64, row, kv_full + s);
+          at_tma_2d(dst + Sm::KV_BYTES + p * Sm::KV_PANEL, &map_v, p * 64, row, kv_full + s);
+        }
       }
     }
   } else if (warp == 1) {
@@ -215,19 +238,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_KEYS >> 3) << 17) |
                                    ((uint32_t)(AT_ROWS >> 4) << 24);
       // T = P V: A = P (K-major over keys), B = V tile [key][d] = MN-major, N = head size
-      constexpr uint32_t idesc_t = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) |
+      constexpr uint32_t idesc_t = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
                                    ((uint32_t)(AT_ROWS >> 4) << 24);
-      const uint32_t q_addr = at_smem(base + AtSmem::Q_OFF);
+      const uint32_t q_addr = at_smem(base + Sm::Q_OFF);
       bool ok = at_wait(q_full, 0);
       if (!ok) atomicExch(status, 12);
       auto issue_s = [&](int j) {
         const int s = j % AT_STAGES;
         if (!at_wait(kv_full + s, (j / AT_STAGES) & 1)) { atomicExch(status, 13); ok = false; return; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t k_addr = at_smem(base + AtSmem::KV_OFF + s * 2 * AtSmem::KV_BYTES);
+        const uint32_t k_addr = at_smem(base + Sm::KV_OFF + s * 2 * Sm::KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < AT_D / 16; ++k)
-          at_mma(tmem + (j & 1) * 64, at_desc(q_addr + k * 32), at_desc(k_addr + k * 32), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < HD / 16; ++k)      // 16 elements of the head per MMA: 32 bytes along a panel's rows
+          at_mma(tmem + (j & 1) * 64, at_desc(q_addr + (k >> 2) * Sm::Q_PANEL + (k & 3) * 32),
+                 at_desc(k_addr + (k >> 2) * Sm::KV_PANEL + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
         at_commit(s_full + (j & 1));
       };
       if (ok && n_tiles > 0) issue_s(0);
@@ -237,10 +261,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!at_wait(p_full + (j & 1), (j >> 1) & 1)) { atomicExch(status, 14); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int s = j % AT_STAGES;
-        const uint32_t v_addr = at_smem(base + AtSmem::KV_OFF + s * 2 * AtSmem::KV_BYTES + AtSmem::KV_BYTES);
+        const uint32_t v_addr = at_smem(base + Sm::KV_OFF + s * 2 * Sm::KV_BYTES + Sm::KV_BYTES);
 #pragma unroll
         for (int k = 0; k < AT_KEYS / 16; ++k)     // 16 keys per MMA: 8 columns of P, 2 groups of 8 V rows
-          at_mma_ts(tmem + 128, tmem + 192 + (j & 1) * 32 + k * 8, at_desc(v_addr + k * 2048), idesc_t,
+          at_mma_ts(tmem + Sh::O_COL, tmem + Sh::p_col(j) + k * 8, at_desc_mn(v_addr + k * 2048, Sm::KV_PANEL), idesc_t,
                     (j > 0 || k > 0) ? 1u : 0u);
         at_commit(o_done);
         at_commit(kv_empty + s);                   // K and V of this stage are read when these MMAs are done
@@ -304,15 +328,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int c0 = 0; c0 < AT_D; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           float t[32];
-          at_ld16(tmem + lane_base + 128 + c0, t);
-          at_ld16(tmem + lane_base + 128 + c0 + 16, t + 16);
+          at_ld16(tmem + lane_base + Sh::O_COL + c0, t);
+          at_ld16(tmem + lane_base + Sh::O_COL + c0 + 16, t + 16);
           at_ld_wait();
 #pragma unroll
           for (int c = 0; c < 32; ++c) t[c] *= corr;
-          at_st16(tmem + lane_base + 128 + c0, t);
-          at_st16(tmem + lane_base + 128 + c0 + 16, t + 16);
+          at_st16(tmem + lane_base + Sh::O_COL + c0, t);
+          at_st16(tmem + lane_base + Sh::O_COL + c0 + 16, t + 16);
         }
         at_st_wait();
       }
@@ -330,8 +354,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // P row: 32 columns of this thread's lane (two keys each)
-      at_st16u(tmem + lane_base + 192 + (j & 1) * 32, packed);
-      at_st16u(tmem + lane_base + 192 + (j & 1) * 32 + 16, packed + 16);
+      at_st16u(tmem + lane_base + Sh::p_col(j), packed);
+      at_st16u(tmem + lane_base + Sh::p_col(j) + 16, packed + 16);
       at_st_wait();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       at_arrive(p_full + (j & 1));
@@ -343,13 +367,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      bf16* dst = out + ((size_t)(q0 + r / G) * H + kh * G + r % G) * AT_D;
+      bf16* dst = out + ((size_t)(q0 + r / G) * H + kh * G + r % G) * HD;
 #pragma unroll
-      for (int c0 = 0; c0 < AT_D; c0 += 32) {
+      for (int c0 = 0; c0 < HD; c0 += 32) {
         float t[32];
         if (n_tiles > 0) {
-          at_ld16(tmem + lane_base + 128 + c0, t);
-          at_ld16(tmem + lane_base + 128 + c0 + 16, t + 16);
+          at_ld16(tmem + lane_base + Sh::O_COL + c0, t);
+          at_ld16(tmem + lane_base + Sh::O_COL + c0 + 16, t + 16);
           at_ld_wait();
         } else {
 #pragma unroll
@@ -411,14 +435,14 @@ AB_API int ab_attention_tc_status() {
   return v;
 }
 
-// 1 if this kernel takes the shape (head size 64, group size a divisor of 128), else 0
+// 1 if this kernel takes the shape (head size 64 or 128, group size a divisor of 128), else 0
 AB_API int ab_attention_prefill_tc_supports(int H, int K, int D) {
-  if (D != AT_D || K <= 0 || H % K) return 0;
+  if ((D != 64 && D != 128) || K <= 0 || H % K) return 0;
   const int G = H / K;
   return (G <= AT_ROWS && AT_ROWS % G == 0) ? 1 : 0;
 }
 
-// qkv [n_tokens, (H+2K)*64] (q part read), out [n_tokens, H*64], cache pages [n_pages, K, 64, 64].
+// qkv [n_tokens, (H+2K)*D] (q part read), out [n_tokens, H*D], cache pages [n_pages, K, 64, D].
 // tile_seq / tile_q0: the tiles of 128/G tokens (sequence, first packed token), as for the mma kernel.
 AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, const void* k_pages, const void* v_pages,
                                    int n_pages, const int* block_table, int table_width, const int* tok_pos,
@@ -434,7 +458,7 @@ AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, con
   {
     cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)(H + 2 * K), (cuuint64_t)n_tokens};
     cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)(H + 2 * K) * D * 2};
-    cuuint32_t box[3] = {(cuuint32_t)D, (cuuint32_t)G, (cuuint32_t)tpt};
+    cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)tpt};          // one panel: 64 elements of the head
     cuuint32_t elem[3] = {1, 1, 1};
     if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(qkv), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -444,19 +468,25 @@ AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, con
   for (int which = 0; which < 2; ++which) {
     cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)n_pages * K * AT_KEYS};
     cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {(cuuint32_t)D, AT_KEYS};
+    cuuint32_t box[2] = {64, AT_KEYS};
     cuuint32_t elem[2] = {1, 1};
     if (enc(which ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(which ? v_pages : k_pages),
             dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return AB_BAD_ARG;
   }
-  cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       AtSmem::TOTAL);
-  if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;
-  e = ab_launch(attention_prefill_tc_kernel, dim3(n_tiles, K), dim3(AT_THREADS), (size_t)AtSmem::TOTAL, stream, mq, mk,
-                mv, (bf16*)out, block_table, table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, scale * AT_LOG2E,
-                window, tpt, status);
+  cudaError_t e;
+#define AT_GO(HDV)                                                                                                   \
+  {                                                                                                                 \
+    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                             AtSmem<HDV>::TOTAL);                                                                   \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
+    e = ab_launch(attention_prefill_tc_kernel<HDV>, dim3(n_tiles, K), dim3(AT_THREADS), (size_t)AtSmem<HDV>::TOTAL, \
+                  stream, mq, mk, mv, (bf16*)out, block_table, table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, \
+                  scale * AT_LOG2E, window, tpt, status);                                                           \
+  }
+  if (D == 64) AT_GO(64) else AT_GO(128)
+#undef AT_GO
   if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;
   return ab_launch_status();
 }

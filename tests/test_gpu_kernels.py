@@ -402,21 +402,27 @@ def test_gemm_tc_swiglu_epilogue(M, F, K, swap, bn):
     assert ops.gemm_tc_status() == 0
 
 
-@pytest.mark.parametrize("H,K", [(4, 4), (8, 2), (32, 8), (16, 1), (6, 6)])
+@pytest.mark.parametrize("H,K,D", [(4, 4, 64), (8, 2, 64), (32, 8, 64), (16, 1, 64), (6, 6, 64),
+                                   (4, 4, 128), (8, 2, 128), (16, 1, 128)])
 @pytest.mark.parametrize("window", [0, 100])
-def test_attention_prefill_tcgen05(H, K, window):
-    """The tcgen05 prefill kernel (head size 64): whole prompts, a chunk on cached tokens, several
-    sequences in one launch; against the float64 reference and against the mma.sync kernel."""
+@pytest.mark.parametrize("growing", [False, True])
+def test_attention_prefill_tcgen05(H, K, D, window, growing):
+    """The tcgen05 prefill kernel (head sizes 64 and 128): whole prompts, a chunk on cached tokens,
+    several sequences in one launch; against the float64 reference and against the mma.sync kernel.
+    `growing`: the keys get longer with their position, so that the rows' maxima keep rising by large
+    steps and the kernel has to move its references and rescale its output again and again."""
     from alpacca_b200 import ops
     from alpacca_b200.cache import KVLayerView
     from types import SimpleNamespace
-    D = 64
     lengths, q_lens = [300, 150, 513], [300, 100, 130]
     table, kp, vp = make_paged(lengths, 20, K, D, torch.bfloat16, seed=H)
     T = sum(q_lens)
     qkv = rnd(T, (H + 2 * K) * D, dtype=torch.bfloat16, seed=7)
     ks = [rnd(n, K, D, dtype=torch.bfloat16, seed=8 + b) for b, n in enumerate(lengths)]
     vs = [rnd(n, K, D, dtype=torch.bfloat16, seed=11 + b) for b, n in enumerate(lengths)]
+    if growing:
+        ks = [(k.float() * (1.0 + torch.arange(k.shape[0], device=k.device).view(-1, 1, 1) / 16.0)).to(torch.bfloat16)
+              for k in ks]
     for b in range(3):
         fill_cache(table.cpu(), kp, vp, b, ks[b], vs[b])
     pos = torch.cat([torch.arange(n - q, n) for n, q in zip(lengths, q_lens)]).to(torch.int32)
