@@ -214,7 +214,10 @@ def gemm_f32(a, w, out, bias=None, n_rows=None):
 GEMV_MAX_ROWS = 8           # up to here the skinny-matrix kernel is the fastest (measured per shape)
 GEMV_NARROW_MAX_ROWS = 16   # ... and up to here for matrices of no more 16-row slabs than the GPU has SMs
 #                             (2048x2048: 4.1 against 5.3 us for the library, 2048x8192: 12.2 against 13.2)
-TC_SWAP_MAX_ROWS = 64       # up to here the tcgen05 kernel with the weights on the 128-row side
+# 9 to 64 rows go to the library product: the tcgen05 product with the weights on the 128-row side
+# (`gemm_tc(swap=True)`) was measured against it at every shape of the 1B and 8B sizes and lost (gate|up
+# with the activation 15.7-20.4 against 14.2-15.5 us, the head 95-106 against 80-98 us): a tcgen05.mma
+# costs the same whatever its N, so 16 to 64 columns waste it.
 TC_PERSISTENT_MIN_ROWS = 1024   # from here the persistent tcgen05 product with the SwiGLU tail beats the library
 #                                 product followed by the activation kernel (16384x2048: 57.9 against 57.8 us at
 #                                 1,024 rows, 100 against 120 at 2,048, 190 against 235 at 4,096)
@@ -455,8 +458,6 @@ def linear_bf16(x, w, out, n_rows=None, bias=None, start_early=True):
     if x.shape[1] % 8 == 0 and (n <= GEMV_MAX_ROWS or (n <= GEMV_NARROW_MAX_ROWS
                                                        and -(-w.shape[0] // 16) <= _sm_count(x.device))):
         return gemv_bf16(x, w, out, bias=bias, n_rows=n, start_early=start_early)
-    if n <= TC_SWAP_MAX_ROWS and out.dtype == torch.float32 and x.shape[1] % 8 == 0:
-        return gemm_tc(x, w, out, bias=bias, n_rows=n, swap=True, slices=1)      # the vocabulary head
     if out.dtype == torch.float32:
         torch.mm(x[:n], w.t(), out_dtype=torch.float32, out=out[:n])
     else:

@@ -79,8 +79,6 @@ class Linear(Part):
         if x.dtype == torch.bfloat16 and self.in_features % 8 == 0:
             if n <= ops.GEMV_MAX_ROWS:
                 return ops.gemv_bf16(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True)
-            if n <= ops.TC_SWAP_MAX_ROWS:
-                return ops.gemm_tc(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, swap=True, slices=1)
             if n >= ops.TC_PERSISTENT_MIN_ROWS:
                 # long prompts: the persistent tcgen05 product with the activation in its tail
                 return ops.gemm_tc(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, swap=False)
