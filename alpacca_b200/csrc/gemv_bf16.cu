@@ -221,7 +221,7 @@ static int launch(const void* X, const void* W, const float* bias, void* Y, floa
   ab_launch(gemv_bf16_kernel<NT, EPI, WARPS>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)X, (const bf16*)W,   \
             bias, Y, partials, arrivals, M, N, K, ldy, gps)
   if (M <= 8) { if (wide) AB_GO(1, 16); else AB_GO(1, GEMV_WARPS); }
-  else if (M <= 16) AB_GO(2, GEMV_WARPS);
+  else if (M <= 16) { if (wide) AB_GO(2, 16); else AB_GO(2, GEMV_WARPS); }
   else AB_GO(4, GEMV_WARPS);
 #undef AB_GO
   return ab_launch_status();
@@ -257,7 +257,7 @@ AB_API int ab_gemv_bf16(const void* X, const void* W, const float* bias, void* Y
   if (slices > 1 && (!partials || !arrivals)) return AB_BAD_ARG;
   if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
   // few slabs and more than one round of loads per warp: 16 warps per CTA
-  const int wide = (M <= 8 && slices == 1 && (N + 15) / 16 <= gemv_sm_count() && K > 8 * GEMV_U * 32) ? 1 : 0;
+  const int wide = (M <= 16 && slices == 1 && (N + 15) / 16 <= gemv_sm_count() && K > 8 * GEMV_U * 32) ? 1 : 0;
   switch (epilogue_kind) {
     case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, wide, stream);
     case EPI_STORE_F32: return launch<EPI_STORE_F32>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, wide, stream);
