@@ -3,9 +3,9 @@
 // MMAs with accumulators in tensor memory (TMEM), operands brought in by TMA with the
 // 128-byte swizzle, softmax in float32 by one thread per query row.
 //
-// A CTA owns 128 query rows of one KV head: the G query heads of the group for 128/G
-// consecutive tokens of one sequence (row r = token q0 + r / G, head kh*G + r % G), so
-// a key tile is fetched once for the whole group.  Keys are visited page by page (a
+// A CTA owns up to 128 query rows of one KV head: the G query heads of the group for
+// floor(128 / G) consecutive tokens of one sequence (row r = token q0 + r / G, head
+// kh*G + r % G; rows past that are idle), so a key tile is fetched once for the whole group.  Keys are visited page by page (a
 // page of the cache, 64 keys of one KV head, is one TMA box).  For tile j:
 //
 //   MMA warp      S_j = Q K_j^T           (M 128, N 64, K = head size)   -> TMEM
@@ -217,7 +217,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (warp == 0) {
     if (lane == 0) {
-      at_expect_tx(q_full, Sm::Q_BYTES);
+      // the box holds tokens_per_tile x G rows (all of them counted, also where they lie past the
+      // sequence's end and are filled with zeros); rows of the tile past the box are never written:
+      // whatever they hold stays in their own rows of S, P and O, which nobody stores
+      at_expect_tx(q_full, Sh::PANELS * tokens_per_tile * G * 128);
       for (int p = 0; p < Sh::PANELS; ++p)
         at_tma_3d(base + Sm::Q_OFF + p * Sm::Q_PANEL, &map_q, p * 64, kh * G, q0, q_full);
       for (int j = 0; j < n_tiles; ++j) {
@@ -435,15 +438,14 @@ AB_API int ab_attention_tc_status() {
   return v;
 }
 
-// 1 if this kernel takes the shape (head size 64 or 128, group size a divisor of 128), else 0
+// 1 if this kernel takes the shape (head size 64 or 128, up to 128 query heads per KV head), else 0
 AB_API int ab_attention_prefill_tc_supports(int H, int K, int D) {
   if ((D != 64 && D != 128) || K <= 0 || H % K) return 0;
-  const int G = H / K;
-  return (G <= AT_ROWS && AT_ROWS % G == 0) ? 1 : 0;
+  return H / K <= AT_ROWS ? 1 : 0;
 }
 
 // qkv [n_tokens, (H+2K)*D] (q part read), out [n_tokens, H*D], cache pages [n_pages, K, 64, D].
-// tile_seq / tile_q0: the tiles of 128/G tokens (sequence, first packed token), as for the mma kernel.
+// tile_seq / tile_q0: the tiles of floor(128 / G) tokens (sequence, first packed token), as for the mma kernel.
 AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, const void* k_pages, const void* v_pages,
                                    int n_pages, const int* block_table, int table_width, const int* tok_pos,
                                    const int* cu_q, const int* tile_seq, const int* tile_q0, int n_tiles, int H,

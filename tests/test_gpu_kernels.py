@@ -402,8 +402,8 @@ def test_gemm_tc_swiglu_epilogue(M, F, K, swap, bn):
     assert ops.gemm_tc_status() == 0
 
 
-@pytest.mark.parametrize("H,K,D", [(4, 4, 64), (8, 2, 64), (32, 8, 64), (16, 1, 64), (6, 6, 64),
-                                   (4, 4, 128), (8, 2, 128), (16, 1, 128)])
+@pytest.mark.parametrize("H,K,D", [(4, 4, 64), (8, 2, 64), (32, 8, 64), (16, 1, 64), (6, 6, 64), (6, 2, 64), (10, 2, 64),
+                                   (4, 4, 128), (8, 2, 128), (16, 1, 128), (12, 2, 128), (7, 1, 128)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("growing", [False, True])
 def test_attention_prefill_tcgen05(H, K, D, window, growing):
