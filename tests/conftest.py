@@ -39,7 +39,7 @@ def model_dirs(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
     for name, cfg, seed in (("a", tiny.TINY_A, 0), ("b", tiny.TINY_B, 1), ("c", tiny.TINY_C, 2),
-                            ("d", tiny.TINY_D, 3)):
+                            ("d", tiny.TINY_D, 3), ("e", tiny.TINY_E, 4)):
         for dt_name, dt in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
             out[(name, dt_name)] = write_random_model_dir(root / f"{name}_{dt_name}", cfg, seed, dtype=dt)
     return out

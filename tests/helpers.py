@@ -8,7 +8,7 @@ import numpy as np
 import plain_llama as plain
 import tiny
 
-CONFIGS = {"a": tiny.TINY_A, "b": tiny.TINY_B, "c": tiny.TINY_C, "d": tiny.TINY_D}
+CONFIGS = {"a": tiny.TINY_A, "b": tiny.TINY_B, "c": tiny.TINY_C, "d": tiny.TINY_D, "e": tiny.TINY_E}
 
 # Largest allowed |engine - plain| on logits.  The plain implementation is float64 on the stored
 # weights.  float32: rounding of float32 sums over at most a few hundred terms, logits of order 1.

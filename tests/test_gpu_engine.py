@@ -10,7 +10,7 @@ from helpers import CONFIGS, check_logits, plain_logits
 pytestmark = pytest.mark.gpu
 
 DTYPES = ("float32", "bfloat16")
-NAMES = ("a", "b", "c", "d")
+NAMES = ("a", "b", "c", "d", "e")
 
 
 def make_engine(model_dir, dtype, max_tokens=64 * 24, max_slots=8, max_positions=None):

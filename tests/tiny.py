@@ -112,6 +112,32 @@ TINY_D = {
 }
 
 
+# A fifth one with the head size of the larger models (128), three query heads on one KV head (a group
+# size that divides nothing), a width that is not heads x head size, and room for prompts of several
+# hundred tokens: head size 128 in the decode kernel and in the kernels that only long prompts reach.
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2,
+    "hidden_size": 80,
+    "num_attention_heads": 3,
+    "num_key_value_heads": 1,
+    "head_dim": 128,
+    "intermediate_size": 104,
+    "vocab_size": 173,
+    "max_position_embeddings": 512,
+    "rms_norm_eps": 2e-6,
+    "rope_theta": 10000.0,
+    "rope_pairing": "llama",
+    "rope_scaling": {"rope_type": "linear", "factor": 4.0},
+    "tie_word_embeddings": False,
+    "attention_bias": False,
+    "mlp_bias": False,
+    "hidden_act": "silu",
+    "bos_token_id": 3,
+    "eos_token_id": 4,
+}
+
+
 def tensor_shapes(cfg: dict) -> dict[str, tuple]:
     """Names and shapes of a checkpoint of this architecture, weights [out, in]."""
     E = cfg["hidden_size"]
