@@ -349,7 +349,7 @@ def run_reference(args):
         sec = time.perf_counter() - t0
     print(json.dumps({
         "metric": "decode tok/s (Llama-3.2-1B shape, 512-token prompt, context 4096)", "impl": "reference",
-        "value": round(steps / sec, 2), "unit": "tok/s", "n_gpus": 0, "steps": steps, "warmup": max(args.warmup, 3),
+        "value": round(steps / sec, 2), "unit": "tok/s", "n_gpus": args.gpus, "device": "cpu (the reference has no GPU path)", "steps": steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(sec / steps * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32 (the reference has no reduced-precision dense path)", "data": "synthetic",
         "config": {"model": "Llama-3.2-1B shape", "layers": L, "global_batch": 1, "prompt_len": PROMPT,
