@@ -8,6 +8,7 @@ reference's counterparts are `prefill` / `forward_batch` / `forward`
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache import CacheFull, SequenceCache
@@ -52,29 +53,37 @@ class Engine:
                 and all(pages <= g.pages.n_free for g in self.cache.kv_groups))
 
     # -- the step ------------------------------------------------------------
-    def _check(self, entries) -> None:
+    def _check(self, entries) -> list:
+        """Refuses a step that the kernels must not see; returns each entry's tokens as an int32 array."""
         if not entries:
             raise ValueError("a step needs at least one sequence")
         seen = set()
+        arrays = []
         for e in entries:
             if e.slot in seen:
                 raise ValueError(f"slot {e.slot} appears twice in one step")
             seen.add(e.slot)
-            if not e.tokens:
+            if len(e.tokens) == 0:
                 raise ValueError(f"slot {e.slot}: a step needs at least one token per sequence")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"token id {t} lies outside the vocabulary of {self.vocab_size}")
+            ids = np.asarray(e.tokens)
+            if ids.ndim != 1 or ids.dtype.kind not in "iu":
+                raise ValueError(f"slot {e.slot}: token ids must be a flat list of integers")
+            lo, hi = int(ids.min()), int(ids.max())
+            if lo < 0 or hi >= self.vocab_size:
+                bad = lo if lo < 0 else hi
+                raise ValueError(f"token id {bad} lies outside the vocabulary of {self.vocab_size}")
+            arrays.append(ids.astype(np.int32, copy=False))
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"slot {e.slot}: wanted place {w} is not among its {len(e.tokens)} tokens")
+        return arrays
 
     def prepare(self, entries) -> StepContext:
-        self._check(entries)
+        arrays = self._check(entries)
         requests = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.reserve(requests)          # raises CacheFull before anything is launched
         lengths = [self.cache.length(e.slot) for e in entries]
-        return self._builder.build(entries, lengths, self.cache)
+        return self._builder.build(entries, lengths, self.cache, arrays)
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Runs one step; returns float32 logits [number of wanted places, vocab] on the device,

@@ -71,7 +71,7 @@ class ContextBuilder:
         self._slot = i
         return buf
 
-    def build(self, entries, lengths, cache) -> StepContext:
+    def build(self, entries, lengths, cache, token_arrays=None) -> StepContext:
         B = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
@@ -84,8 +84,9 @@ class ContextBuilder:
         total = offs[-1]
         stage = self._staging(total)
         host = stage.numpy()
-        tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int32, count=T)
-        host[offs[0]:offs[0] + T] = tokens
+        if token_arrays is None:
+            token_arrays = [np.asarray(e.tokens, dtype=np.int32) for e in entries]
+        host[offs[0]:offs[0] + T] = token_arrays[0] if B == 1 else np.concatenate(token_arrays)
         cu = np.zeros(B + 1, dtype=np.int32)
         np.cumsum(q_lens, out=cu[1:])
         host[offs[1]:offs[1] + T] = np.repeat(np.arange(B, dtype=np.int32), q_lens)

@@ -27,7 +27,16 @@ def _lib(name):
     return build.load(name)
 
 
+# torch's current stream of the current device as a raw handle.  The direct bindings cost a
+# fraction of a microsecond; torch.cuda.current_stream() builds a Stream object each time
+# (15 us, and a prefill step asks a hundred times).
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -42,9 +51,9 @@ def _need(cond, msg):
 
 def _cuda(*tensors):
     for t in tensors:
-        if t is not None:
-            _need(t.is_cuda, "alpacca_b200 kernels run on CUDA tensors only (there is no CPU path); "
-                  f"got a tensor on {t.device}")
+        if t is not None and not t.is_cuda:
+            raise KernelError("alpacca_b200 kernels run on CUDA tensors only (there is no CPU path); "
+                              f"got a tensor on {t.device}")
 
 
 launches = 0     # kernels of this package launched so far (the benchmark reports the count)
@@ -60,14 +69,17 @@ def _check(rc, what):
 
 
 def _dt(t):
-    _need(t.dtype in _DT, f"dtype {t.dtype} is not supported by the kernels (float32 or bfloat16)")
-    return _DT[t.dtype]
+    code = _DT.get(t.dtype)
+    if code is None:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels (float32 or bfloat16)")
+    return code
 
 
 def _i32(t, n=None, name="index tensor"):
-    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
-    if n is not None:
-        _need(t.numel() >= n, f"{name} holds {t.numel()} entries, {n} needed")
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+    if n is not None and t.numel() < n:
+        raise KernelError(f"{name} holds {t.numel()} entries, {n} needed")
 
 
 # ---------------------------------------------------------------------------
@@ -458,13 +470,16 @@ def linear_bf16(x, w, out, n_rows=None, bias=None, start_early=True):
     if x.shape[1] % 8 == 0 and (n <= GEMV_MAX_ROWS or (n <= GEMV_NARROW_MAX_ROWS
                                                        and -(-w.shape[0] // 16) <= _sm_count(x.device))):
         return gemv_bf16(x, w, out, bias=bias, n_rows=n, start_early=start_early)
+    xs, ys = (x, out) if n == x.shape[0] == out.shape[0] else (x[:n], out[:n])
     if out.dtype == torch.float32:
-        torch.mm(x[:n], w.t(), out_dtype=torch.float32, out=out[:n])
+        torch.mm(xs, w.t(), out_dtype=torch.float32, out=ys)
     else:
-        torch.mm(x[:n], w.t(), out=out[:n])
+        torch.mm(xs, w.t(), out=ys)
     if bias is not None:
-        add_bias(out[:n], bias)
+        add_bias(ys, bias)
     return out
+
+
 def repeat_penalty(logits, recent, penalty):
     """In place: for each distinct token of a row's window (int32 [B,R], -1 = unused),
     l > 0 -> l / penalty, else l * penalty."""
