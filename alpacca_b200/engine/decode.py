@@ -115,7 +115,7 @@ class _Shape:
             n_tokens=self.rows, n_seqs=self.rows, n_want=self.rows, is_decode=True, max_q_len=1,
             max_kv_len=self.width * PAGE_SIZE, tokens=self.d("tokens"), tok_seq=self.d("tok_seq"),
             tok_pos=self.d("tok_pos"), cu_q=self.d("cu_q"), kv_len=self.d("kv_len"), slots=self.d("slots"),
-            want_rows=self.d("want_rows"), block_tables=self.tables_dev())
+            want_rows=self.d("want_rows"), block_tables=self.tables_dev(), wants_every_row=True)
 
 
 class GraphDecoder:

@@ -95,6 +95,20 @@ class DecoderModel(Part):
             n += k
         return n
 
+    def _reader_after(self, i: int, ctx):
+        """The norm that reads the stream after run `i`, if what follows accepts rows prepared for it
+        (`OwedNorm`) in this step: the next block's first norm, or the last norm before the head (only
+        if every row's logits are wanted, in order)."""
+        s = self.spec
+        if i + 1 < len(s.schedule):
+            first = getattr(s.layers[s.schedule[i + 1].layer], "first_norm", None)
+            return first(ctx.n_tokens) if first is not None else None
+        accepts = getattr(s.head, "accepts_owed_norm", None)
+        if (ctx.wants_every_row and accepts is not None and accepts(ctx.n_tokens)
+                and s.final_norm.deferred() is not None):
+            return s.final_norm
+        return None
+
     def forward(self, ctx, cache) -> torch.Tensor:
         """Runs the step described by `ctx`; returns float32 logits [n_want, vocab]."""
         s = self.spec
@@ -103,8 +117,15 @@ class DecoderModel(Part):
             s.position.add_to_embeddings(stream.residual, ctx)
         for i, run in enumerate(s.schedule):
             view = cache.entry_view(self.entry_of_run[i], ctx.block_tables)
+            stream.next_norm = self._reader_after(i, ctx)
             s.layers[run.layer].forward(stream, ctx, view, write_cache=run.reads_entry_of is None)
+        stream.next_norm = None
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=stream.residual.device)
-        h = s.final_norm.forward(stream.residual, stream.delta, rows=ctx.want_rows, n_rows=ctx.n_want)
+        if stream.owed is not None:
+            if stream.owed.norm is not s.final_norm:
+                raise RuntimeError("rows were prepared for another norm than the last one")
+            h, stream.owed = stream.owed, None
+        else:
+            h = s.final_norm.forward(stream.residual, stream.delta, rows=ctx.want_rows, n_rows=ctx.n_want)
         return s.head.forward(h, n_rows=ctx.n_want)[:ctx.n_want]

@@ -39,6 +39,7 @@ class StepContext:
     host_slots: list = None      # the same facts on the host, for parts that plan on the host
     host_q_lens: list = None
     host_kv_lens: list = None
+    wants_every_row: bool = False    # want_rows is 0, 1, .., n_tokens - 1: each row's logits, in order
     extras: dict = field(default_factory=dict)   # per-step plans of kernels (tile lists and the like)
 
 
@@ -116,4 +117,6 @@ class ContextBuilder:
             tokens=part(0, T), tok_seq=part(1, T), tok_pos=part(2, T), cu_q=part(3, B + 1),
             kv_len=part(4, B), slots=part(5, B), want_rows=part(6, n_want),
             block_tables=[dev[offs[7 + g]:offs[7 + g] + B * w].view(B, w) for g, w in enumerate(widths)],
-            host_slots=[e.slot for e in entries], host_q_lens=q_lens, host_kv_lens=kv.tolist())
+            host_slots=[e.slot for e in entries], host_q_lens=q_lens, host_kv_lens=kv.tolist(),
+            wants_every_row=all(len(e.want) == q and all(w == i for i, w in enumerate(e.want))
+                                for e, q in zip(entries, q_lens)))

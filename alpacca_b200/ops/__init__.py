@@ -225,6 +225,7 @@ def gemm_f32(a, w, out, bias=None, n_rows=None):
 
 GEMV_MAX_ROWS = 8           # up to here the skinny-matrix kernel is the fastest (measured per shape)
 GEMV_NARROW_MAX_ROWS = 16   # ... and up to here for matrices of no more 16-row slabs than the GPU has SMs
+DEFER_NORM = True           # steps of up to GEMV_MAX_ROWS rows: RMS norms run inside the products around them
 #                             (2048x2048: 4.1 against 5.3 us for the library, 2048x8192: 12.2 against 13.2)
 # 9 to 64 rows go to the library product: the tcgen05 product with the weights on the 128-row side
 # (`gemm_tc(swap=True)`) was measured against it at every shape of the 1B and 8B sizes and lost (gate|up
@@ -243,31 +244,58 @@ def _sm_count(device) -> int:
     return n
 
 
-def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None, start_early=True):
+def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None, start_early=True, owed=None,
+              residual=None, norm_weight=None):
     """out[:n] = x[:n] @ w^T (+ bias) for n <= 32 rows, bfloat16 x [M,K], w [N,K].
 
     out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row interleaved gate|up
     matrix [2F,K] and out is bfloat16 [M,F] = silu(gate) * up.  `start_early` off: the kernel is
     launched without programmatic dependent launch, i.e. after the kernel before it has ended (for
     the product that follows the decode attention, see csrc/launch.cuh).
+
+    The RMS norm between two products without a kernel of its own (see csrc/gemv_bf16.cu):
+    `owed` = (ss float32 [M, n_part], width, eps): x's rows still owe the division by
+    sqrt(sum(ss[m]) / width + eps), which is applied to the sums.  `residual` (float32 [M,N]) with
+    `norm_weight` (float32 [N]): the result is added to the residual in place, out becomes
+    bf16(residual * norm_weight) and the partial sums of the residual's squares are returned as
+    float32 [M, ceil(N / 16)] (the `ss` of the next product's `owed`).
     """
-    _cuda(x, w, out, bias)
+    _cuda(x, w, out, bias, residual, norm_weight)
     n = x.shape[0] if n_rows is None else n_rows
     K = x.shape[1]
     N = w.shape[0]
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
           and w.dim() == 2 and w.shape[1] == K and out.is_contiguous(), "gemv_bf16: x [M,K], w [N,K] bfloat16")
-    _need(0 < n <= 32 and n <= x.shape[0] and n <= out.shape[0], f"gemv_bf16 takes 1..32 rows, got {n}")
-    _need(K % 8 == 0, f"gemv_bf16: the inner size {K} must be a multiple of 8")
+    if not (0 < n <= 32 and n <= x.shape[0] and n <= out.shape[0]):
+        raise KernelError(f"gemv_bf16 takes 1..32 rows, got {n}")
+    if K % 8:
+        raise KernelError(f"gemv_bf16: the inner size {K} must be a multiple of 8")
+    ss_out = None
     if swiglu:
+        _need(residual is None, "gemv_bf16: the activation and the residual epilogue exclude each other")
         _need(N % 16 == 0 and out.dtype == torch.bfloat16 and out.shape[-1] == N // 2,
               "gemv_bf16 swiglu: w [2F,K] with F a multiple of 8, out bfloat16 [M,F]")
         epi = 2
+    elif residual is not None:
+        _need(out.shape[-1] == N and out.dtype == torch.bfloat16, "gemv_bf16 residual: out bfloat16 [M,N]")
+        _need(residual.dtype == torch.float32 and residual.is_contiguous() and residual.shape[-1] == N
+              and residual.numel() >= n * N, "gemv_bf16 residual: float32 [M,N]")
+        _need(norm_weight is not None and norm_weight.dtype == torch.float32 and norm_weight.numel() == N
+              and norm_weight.is_contiguous(), "gemv_bf16 residual: norm weight float32 [N]")
+        ss_out = torch.empty((out.shape[0], -(-N // 16)), dtype=torch.float32, device=x.device)
+        epi = 3
     else:
         _need(out.shape[-1] == N and out.dtype in (torch.bfloat16, torch.float32), "gemv_bf16: out [M,N]")
         epi = 1 if out.dtype == torch.float32 else 0
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemv_bf16: bias f32 [N]")
+    ss_in, n_part, inv_width, eps = None, 0, 0.0, 0.0
+    if owed is not None:
+        ss_in, width, eps = owed
+        _cuda(ss_in)
+        _need(ss_in.dtype == torch.float32 and ss_in.dim() == 2 and ss_in.is_contiguous() and ss_in.shape[0] >= n
+              and width > 0, "gemv_bf16: owed sums of squares float32 [M, n_part]")
+        n_part, inv_width = ss_in.shape[1], 1.0 / width
     lib = _lib("gemv_bf16")
     if slices is None:
         slices = lib.ab_gemv_bf16_slices(N, K, _sm_count(x.device))
@@ -280,12 +308,14 @@ def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None, star
     if not start_early:
         lib.ab_pdl_hold(1)
     try:
-        _check(lib.ab_gemv_bf16(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K, out.shape[-1],
-                                epi, slices, _stream()), "gemv_bf16")
+        _check(lib.ab_gemv_bf16_norm(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K,
+                                     out.shape[-1], epi, slices, _p(ss_in), n_part, ctypes.c_float(inv_width),
+                                     ctypes.c_float(eps), _p(residual), _p(norm_weight), _p(ss_out), _stream()),
+               "gemv_bf16")
     finally:
         if not start_early:
             lib.ab_pdl_hold(0)
-    return out
+    return out if ss_out is None else (out, ss_out)
 
 
 def _prefill_tiles(ctx, G, device, rows=64):
@@ -456,7 +486,21 @@ def rope_attention(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, wri
     return attention(qkv, out, cache, ctx, H, K, D, scale, window)
 
 
-def linear_bf16(x, w, out, n_rows=None, bias=None, start_early=True):
+def defers_norm(n_rows: int, width: int) -> bool:
+    """Whether the product before a norm of a `width`-wide stream can leave `n_rows` rows prepared for
+    the product after it (both must be the skinny product, see `gemv_bf16`)."""
+    return DEFER_NORM and 0 < n_rows <= GEMV_MAX_ROWS and width % 8 == 0
+
+
+def owed_norm_pays(n_rows: int, out_features: int, in_features: int, device) -> bool:
+    """Whether the product [out_features, in_features] after a norm should finish the norm itself in a
+    step of `n_rows` rows: only where its 16-row slabs are all resident at once (two CTAs per
+    processor).  A grid of several waves loses more by the added tail of every CTA than the norm's
+    kernel costs (measured, see csrc/gemv_bf16.cu)."""
+    return (defers_norm(n_rows, in_features) and -(-out_features // 16) <= 2 * _sm_count(device))
+
+
+def linear_bf16(x, w, out, n_rows=None, bias=None, start_early=True, owed=None):
     """out[:n] = x[:n] @ w^T (+ bias) for bfloat16 x [M,K], w [N,K]; out bfloat16 or float32 [M,N].
 
     Up to GEMV_MAX_ROWS rows (decode steps; GEMV_NARROW_MAX_ROWS for narrow matrices): the
@@ -469,7 +513,8 @@ def linear_bf16(x, w, out, n_rows=None, bias=None, start_early=True):
           "linear_bf16: x [M,K], w [N,K], out [M,N]")
     if x.shape[1] % 8 == 0 and (n <= GEMV_MAX_ROWS or (n <= GEMV_NARROW_MAX_ROWS
                                                        and -(-w.shape[0] // 16) <= _sm_count(x.device))):
-        return gemv_bf16(x, w, out, bias=bias, n_rows=n, start_early=start_early)
+        return gemv_bf16(x, w, out, bias=bias, n_rows=n, start_early=start_early, owed=owed)
+    _need(owed is None, "linear_bf16: only the skinny product finishes a norm that its input owes")
     xs, ys = (x, out) if n == x.shape[0] == out.shape[0] else (x[:n], out[:n])
     if out.dtype == torch.float32:
         torch.mm(xs, w.t(), out_dtype=torch.float32, out=ys)

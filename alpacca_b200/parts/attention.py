@@ -37,13 +37,18 @@ class Attention(Mixer):
     def cache_spec(self):
         return KVSpec(self.K, self.D, self.window)
 
-    def forward(self, h, ctx, cache, write_cache: bool = True):
+    adds_to_residual = True
+
+    def accepts_owed_norm(self, n_rows: int) -> bool:
+        return self.qkv.accepts_owed_norm(n_rows)
+
+    def forward(self, h, ctx, cache, write_cache: bool = True, then=None):
         T = ctx.n_tokens
         qkv = self.qkv.forward(h, n_rows=T)
         rot = self.position.rotation() if self.position is not None else None
-        att = torch.empty((h.shape[0], self.H * self.D), dtype=h.dtype, device=h.device)
+        att = torch.empty((qkv.shape[0], self.H * self.D), dtype=qkv.dtype, device=qkv.device)
         ops.rope_attention(qkv, att, cache, ctx, self.H, self.K, self.D, self.scale, self.window or 0, rot,
                            write_cache=write_cache)
         # the attention kernel fills the SMs' shared memory, the product wants it as L1: it starts
         # when the attention has ended, not while it runs
-        return self.out.forward(att, n_rows=T, start_early=False)
+        return self.out.forward(att, n_rows=T, start_early=False, then=then)

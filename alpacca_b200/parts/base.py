@@ -13,6 +13,15 @@ part knows which model it is in: it never reads a configuration object.
 `ctx` is the step's `StepContext` (device index tensors of the packed batch);
 `cache` is what the mixer's `cache_spec()` asked for, for the cache entry that
 the schedule gives this run of the layer: a `KVLayerView` or a `StateLayerView`.
+
+A norm without a kernel of its own (optional; steps of a few rows).  A norm whose
+`deferred()` gives (weight, width, eps) is one factor per row, 1 / rms, times a weight per
+column, so the product before it and the product after it can share its work.  A mixer or
+feed-forward that sets `adds_to_residual` accepts `then=(residual, norm)`: it may add its output
+to the residual itself and return an `OwedNorm` for `norm` instead of a delta (or a plain delta
+when it cannot, e.g. for many rows).  One whose `accepts_owed_norm(n_rows)` says yes takes an
+`OwedNorm` as its input `h` in a step of that many rows.  Parts that define neither never see
+either; the block then runs the norm's own kernel.
 """
 from __future__ import annotations
 
@@ -45,6 +54,31 @@ class StateSpec:
     """The mixer keeps a state of fixed shape per sequence (zero at a sequence's start)."""
     shape: tuple
     dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class OwedNorm:
+    """Rows whose RMS norm the reading product finishes: `x` holds residual * norm weight in the
+    activation dtype, `ss` [rows, n_part] float32 partial sums of the residual's squares; every
+    row still owes the division by sqrt(sum(ss[row]) / width + eps).  `norm` is the norm it
+    stands for."""
+    x: torch.Tensor
+    ss: torch.Tensor
+    width: int
+    eps: float
+    norm: object = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def device(self):
+        return self.x.device
 
 
 class Part:
@@ -86,8 +120,20 @@ class Norm(Part):
         """normed(residual + delta); adds delta into the residual unless `rows` picks rows."""
         raise NotImplementedError
 
+    def deferred(self):
+        """(weight float32 [width], width, eps) if this norm is residual * weight / rms(residual)
+        and may be finished by the product that reads it (see `OwedNorm`), else None."""
+        return None
+
 
 class Mixer(Part):
+    #: `forward` accepts `then=(residual, norm)` (see the head of this file)
+    adds_to_residual = False
+
+    def accepts_owed_norm(self, n_rows: int) -> bool:
+        """Whether `forward` takes an `OwedNorm` as `h` in a step of `n_rows` rows."""
+        return False
+
     def cache_spec(self) -> KVSpec | StateSpec | None:
         return None
 
@@ -96,6 +142,11 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    adds_to_residual = False
+
+    def accepts_owed_norm(self, n_rows: int) -> bool:
+        return False
+
     def forward(self, h, ctx):
         raise NotImplementedError
 

@@ -22,7 +22,12 @@ class SwiGLU(FeedForward):
                               interleave8=True)
         self.down = Linear(opts, inner, [(f"{prefix}.{d}", width)], bias=bias)
 
-    def forward(self, h, ctx):
+    adds_to_residual = True
+
+    def accepts_owed_norm(self, n_rows: int) -> bool:
+        return self.gate_up.accepts_owed_norm(n_rows)
+
+    def forward(self, h, ctx, then=None):
         T = ctx.n_tokens
         act = self.gate_up.forward_swiglu(h, n_rows=T)
-        return self.down.forward(act, n_rows=T)
+        return self.down.forward(act, n_rows=T, then=then)

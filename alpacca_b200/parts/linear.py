@@ -12,7 +12,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import ParamSpec
-from .base import BuildOptions, Part
+from .base import BuildOptions, OwedNorm, Part
 
 
 class Linear(Part):
@@ -62,19 +62,43 @@ class Linear(Part):
         """Uses an existing tensor as the matrix (a tied head)."""
         self.weight = tensor
 
-    def forward(self, x: torch.Tensor, n_rows: int | None = None, start_early: bool = True) -> torch.Tensor:
+    def accepts_owed_norm(self, n_rows: int) -> bool:
+        """Whether `forward` should be given an `OwedNorm` in a step of `n_rows` rows (it can take one
+        whenever the skinny product runs; it pays only for some shapes, see `ops.owed_norm_pays`)."""
+        return (self.opts.dtype == torch.bfloat16 and self.weight is not None
+                and ops.owed_norm_pays(n_rows, self.out_features, self.in_features, self.weight.device))
+
+    def forward(self, x, n_rows: int | None = None, start_early: bool = True, then=None):
         """`start_early` off: the product's kernel may not start before the kernel before it has ended
-        (see `ops.gemv_bf16`)."""
+        (see `ops.gemv_bf16`).  `x` may be an `OwedNorm` (the division by the rms is applied to the
+        sums).  `then` = (residual, norm): where the step has few enough rows, the result is added to
+        the residual here and an `OwedNorm` for `norm` is returned instead of the result."""
         n = x.shape[0] if n_rows is None else n_rows
+        owed = None
+        if isinstance(x, OwedNorm):
+            owed, x = (x.ss, x.width, x.eps), x.x
+        if then is not None and x.dtype == torch.bfloat16 and self.out_dtype == torch.bfloat16:
+            residual, norm = then
+            d = norm.deferred()
+            if (d is not None and d[1] == self.out_features and ops.defers_norm(n, self.out_features)
+                    and self.in_features % 8 == 0):
+                out = torch.empty((x.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
+                _, ss = ops.gemv_bf16(x, self.weight, out, bias=self.bias, n_rows=n, start_early=start_early,
+                                      owed=owed, residual=residual, norm_weight=d[0])
+                return OwedNorm(out, ss, d[1], d[2], norm)
         out = torch.empty((x.shape[0], self.out_features), dtype=self.out_dtype, device=x.device)
         if x.dtype == torch.float32:
             ops.gemm_f32(x, self.weight, out, bias=self.bias, n_rows=n)
             return out
-        return ops.linear_bf16(x, self.weight, out, n_rows=n, bias=self.bias, start_early=start_early)
+        return ops.linear_bf16(x, self.weight, out, n_rows=n, bias=self.bias, start_early=start_early, owed=owed)
 
-    def forward_swiglu(self, x: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
+    def forward_swiglu(self, x, n_rows: int | None = None) -> torch.Tensor:
         """silu(gate) * up of the interleaved gate|up product, [M, out_features / 2]."""
         n = x.shape[0] if n_rows is None else n_rows
+        if isinstance(x, OwedNorm):
+            act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
+            return ops.gemv_bf16(x.x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True,
+                                 owed=(x.ss, x.width, x.eps))
         act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
         if x.dtype == torch.bfloat16 and self.in_features % 8 == 0:
             if n <= ops.GEMV_MAX_ROWS:

@@ -23,6 +23,11 @@ class RMSNorm(Norm):
     def load_own(self, fetch):
         self.weight = fetch(self.own_param_specs()[0])
 
+    def deferred(self):
+        if self.opts.dtype != torch.bfloat16 or self.weight is None:
+            return None
+        return self.weight, self.width, self.eps
+
     def forward(self, residual, delta, out=None, rows=None, n_rows=None):
         if out is None:
             n = (rows.numel() if rows is not None else residual.shape[0]) if n_rows is None else n_rows

@@ -176,3 +176,30 @@ def test_padding_and_batch_do_not_change_a_result(model_dirs, dtype):
     else:
         assert np.abs(alone - both).max() <= 2e-2 and np.abs(alone - cut).max() <= 4e-2
     check_logits(cut, plain_logits(d, toks), dtype, "cut into steps")
+
+
+@pytest.mark.parametrize("name", ["b", "e"])
+def test_norms_inside_the_products_change_no_result(model_dirs, name, monkeypatch):
+    """Steps of a few rows run the RMS norms inside the products before and after them.  With that
+    switched off the same logits come out, within bfloat16 rounding, from more kernels."""
+    from alpacca_b200 import ops
+    from alpacca_b200.engine import StepEntry
+    d = model_dirs[(name, "bfloat16")]
+    cfg = CONFIGS[name]
+    seqs = [tiny.prompt_tokens(cfg, n, 700 + i) for i, n in enumerate((30, 9, 17))]
+    want = [plain_logits(d, s) for s in seqs]
+    runs = {}
+    for defer in (True, False):
+        monkeypatch.setattr(ops, "DEFER_NORM", defer)
+        eng = make_engine(d, "bfloat16")
+        slots = [eng.alloc_slot() for _ in seqs]
+        eng.step([StepEntry(slot, s[:-6], []) for slot, s in zip(slots, seqs)])
+        before, got = ops.launches, []
+        for p in range(6, 0, -1):
+            got.append(eng.step([StepEntry(slot, [s[-p]], [0]) for slot, s in zip(slots, seqs)]).cpu().numpy())
+        runs[defer] = (np.stack(got), ops.launches - before)
+        for i, p in enumerate(range(6, 0, -1)):
+            for b in range(len(seqs)):
+                check_logits(got[i][b], want[b][len(seqs[b]) - p], "bfloat16", f"{name} defer={defer} step {i} seq {b}")
+    assert runs[True][1] < runs[False][1], "the norms still ran as kernels of their own"
+    assert np.abs(runs[True][0] - runs[False][0]).max() <= 4e-2

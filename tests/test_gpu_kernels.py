@@ -369,6 +369,52 @@ def test_gemv_bf16_swiglu_epilogue(M, F, K):
     close(out, g / (1 + torch.exp(-g)) * u, "bfloat16", "swiglu epilogue")
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 32])
+@pytest.mark.parametrize("E,K,N2,slices", [(72, 200, 88, 1), (2048, 264, 1003, 1), (200, 8200, 72, 1),
+                                           (4104, 128, 160, 1), (264, 4096, 520, 3)])
+def test_gemv_bf16_norm_between_two_products(M, E, K, N2, slices):
+    """The residual epilogue (add to the 32-bit residual, bf16(residual * norm weight), partial sums of
+    squares) and the product after it that applies the owed division by the rms: together they are
+    product, residual add, RMS norm (alpacca/tensor.py:163-173), product; also with the activation."""
+    from alpacca_b200 import ops
+    eps = 3e-4
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w1, b1 = rnd(E, K, dtype=torch.bfloat16, seed=2, scale=0.1), rnd(E, seed=3)
+    res0 = rnd(M, E, seed=4, scale=2.0)
+    nw = 1.0 + rnd(E, seed=5, scale=0.3)
+    w2, b2 = rnd(N2, E, dtype=torch.bfloat16, seed=6, scale=0.1), rnd(N2, seed=7)
+    want_res = res0.double() + x.double() @ w1.double().T + b1.double()
+    rms = torch.sqrt((want_res ** 2).mean(-1, keepdim=True) + eps)
+    normed = want_res / rms * nw.double()
+    want = normed @ w2.double().T + b2.double()
+
+    res = res0.clone()
+    xw = torch.full((M, E), 9.0, dtype=torch.bfloat16, device="cuda")
+    _, ss = ops.gemv_bf16(x, w1, xw, bias=b1, residual=res, norm_weight=nw, slices=slices)
+    close(res, want_res, "float32", "residual after the product")
+    assert tuple(ss.shape) == (M, -(-E // 16))
+    close(ss.sum(-1), (want_res ** 2).sum(-1), "float32", "sums of squares")
+    close(xw, want_res * nw.double(), "bfloat16", "residual times the norm weight")
+    owed = (ss, E, eps)
+    for dt in (torch.float32, torch.bfloat16):
+        out = torch.full((M, N2), 9.0, dtype=dt, device="cuda")
+        ops.gemv_bf16(xw, w2, out, bias=b2, owed=owed)
+        close(out, want, "bfloat16", f"product after the norm {dt}")
+    if N2 % 16 == 0:
+        F = N2 // 2
+        g = want.view(M, F // 8, 2, 8)[:, :, 0].reshape(M, F)
+        u = want.view(M, F // 8, 2, 8)[:, :, 1].reshape(M, F)
+        out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+        ops.gemv_bf16(xw, w2, out, bias=b2, swiglu=True, owed=owed)
+        close(out, g / (1 + torch.exp(-g)) * u, "bfloat16", "activation after the norm")
+    # fewer rows than the buffers hold: the rest of the residual is left alone
+    if M > 1:
+        res = res0.clone()
+        ops.gemv_bf16(x, w1, xw, bias=b1, residual=res, norm_weight=nw, n_rows=M - 1)
+        assert torch.equal(res[M - 1], res0[M - 1])
+        close(res[:M - 1], want_res[:M - 1], "float32")
+
+
 @pytest.mark.parametrize("M,N,K,swap,bn,slices", [
     (128, 256, 64, False, 256, 1), (300, 520, 328, False, 128, 1), (2048, 1024, 512, False, 256, 1),
     (8, 128, 128, True, 16, 1), (13, 1003, 200, True, 16, 1), (33, 520, 264, True, 64, 1),
