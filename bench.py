@@ -281,7 +281,7 @@ def run_reference(args):
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "alpacca" / "model.py").is_file():
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference "
-                          "(pip install --no-index --target baseline/_ref /root/reference)"}))
+                          "(pip install --no-index --no-build-isolation --target baseline/_ref <the reference's source tree>)"}))
         return 0
     sys.path.insert(0, str(ref))
     try:
