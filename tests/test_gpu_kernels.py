@@ -415,6 +415,21 @@ def test_gemv_bf16_norm_between_two_products(M, E, K, N2, slices):
         close(res[:M - 1], want_res[:M - 1], "float32")
 
 
+@pytest.mark.parametrize("M,N,K", [(3, 1003, 120), (8, 70, 64), (16, 2050, 264)])
+def test_gemv_bf16_residual_epilogue_at_odd_widths(M, N, K):
+    """The residual epilogue where the stream's width is no multiple of 4 (the tile of the residual is
+    then read straight from memory, not staged) and the last slab is partial."""
+    from alpacca_b200 import ops
+    x, w, b = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.1), rnd(N, seed=3)
+    res0, nw = rnd(M, N, seed=4, scale=2.0), 1.0 + rnd(N, seed=5, scale=0.3)
+    want = res0.double() + x.double() @ w.double().T + b.double()
+    res, xw = res0.clone(), torch.full((M, N), 9.0, dtype=torch.bfloat16, device="cuda")
+    _, ss = ops.gemv_bf16(x, w, xw, bias=b, residual=res, norm_weight=nw)
+    close(res, want, "float32", "residual")
+    close(xw, want * nw.double(), "bfloat16", "residual times the norm weight")
+    close(ss.sum(-1), (want ** 2).sum(-1), "float32", "sums of squares")
+
+
 @pytest.mark.parametrize("M,N,K,swap,bn,slices", [
     (128, 256, 64, False, 256, 1), (300, 520, 328, False, 128, 1), (2048, 1024, 512, False, 256, 1),
     (8, 128, 128, True, 16, 1), (13, 1003, 200, True, 16, 1), (33, 520, 264, True, 64, 1),
