@@ -209,9 +209,10 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
-  const int b = tile_seq[blockIdx.x];
-  const int q0 = tile_q0[blockIdx.x];
-  const int kh = blockIdx.y;
+  // tile by tile (longest key ranges first), the KV heads of a tile side by side: CTAs start in index order
+  const int tile = blockIdx.x / K, kh = blockIdx.x - tile * K;
+  const int b = tile_seq[tile];
+  const int q0 = tile_q0[tile];
   const int q_end = cu_q[b + 1];
   const int n_tok = min(tokens_per_tile, q_end - q0);
   const int n_rows = n_tok * G;
@@ -766,7 +767,8 @@ AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, c
   if (tokens_per_tile < 1 || tokens_per_tile * G > 64) return AB_BAD_ARG;
   const int pitch = D + 8;
   const size_t smem = (size_t)(64 + 4 * 64) * pitch * sizeof(bf16);
-  dim3 grid(n_tiles, K);
+  if ((long long)n_tiles * K > 0x7fffffffLL) return AB_BAD_ARG;
+  dim3 grid((unsigned)n_tiles * K);
   const float sl = scale * LOG2E;
 #define AB_GO(DM)                                                                                                  \
   {                                                                                                                \

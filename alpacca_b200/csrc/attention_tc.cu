@@ -182,9 +182,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = H / K;
-  const int b = tile_seq[blockIdx.x];
-  const int q0 = tile_q0[blockIdx.x];
-  const int kh = blockIdx.y;
+  // CTAs start in the order of their index: tile by tile (the longest key ranges first), the KV heads
+  // of a tile side by side, so that no long tile is left for the end (by KV head first, the last heads'
+  // longest tiles started when most of the device had run dry: 53 us per layer instead of 44)
+  const int tile = blockIdx.x / K, kh = blockIdx.x - tile * K;
+  const int b = tile_seq[tile];
+  const int q0 = tile_q0[tile];
   const int q_end = cu_q[b + 1];
   const int n_tok = min(tokens_per_tile, q_end - q0);
   const int n_rows = n_tok * G;
@@ -451,7 +454,7 @@ AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, con
                                    const int* cu_q, const int* tile_seq, const int* tile_q0, int n_tiles, int H,
                                    int K, int D, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return AB_OK;
-  if (!ab_attention_prefill_tc_supports(H, K, D) || K > 65535) return AB_BAD_ARG;
+  if (!ab_attention_prefill_tc_supports(H, K, D) || (long long)n_tiles * K > 0x7fffffffLL) return AB_BAD_ARG;
   AtEncodeFn enc = at_encode_fn();
   int* status = at_status_word();
   if (!enc || !status) return AB_BAD_ARG;
@@ -483,7 +486,7 @@ AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, con
     e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
                              AtSmem<HDV>::TOTAL);                                                                   \
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
-    e = ab_launch(attention_prefill_tc_kernel<HDV>, dim3(n_tiles, K), dim3(AT_THREADS), (size_t)AtSmem<HDV>::TOTAL, \
+    e = ab_launch(attention_prefill_tc_kernel<HDV>, dim3((unsigned)n_tiles * K), dim3(AT_THREADS), (size_t)AtSmem<HDV>::TOTAL, \
                   stream, mq, mk, mv, (bf16*)out, block_table, table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, \
                   scale * AT_LOG2E, window, tpt, status);                                                           \
   }
