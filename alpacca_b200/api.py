@@ -42,6 +42,7 @@ class Model:
         self._decoders: dict = {}
         self._slot = None            # the single sequence of prefill()/forward()/reset()
         self.cached_ids: list[int] = []
+        self.last_prefill_forwarded = 0    # tokens the last prefill() ran (alpacca/model.py:612,628)
 
     # -- loading -----------------------------------------------------------
     @staticmethod
@@ -55,7 +56,7 @@ class Model:
         reference: 0 = min(trained context, 4096), else min(n_ctx, trained context)."""
         from .config import load_config
         t0 = time.time()
-        trained = getattr(load_config(path), "max_position_embeddings", DEFAULT_CTX)
+        trained = load_config(path).max_positions or DEFAULT_CTX
         ctx = cls._context(n_ctx, trained)
         decoder = load_model_dir(path, resolve_dtype(dtype), device, max_positions=ctx)
         m = cls(decoder, ctx, max_batch, max_tokens)
@@ -70,7 +71,7 @@ class Model:
         t0 = time.time()
         if isinstance(config, dict):
             config = config_from_dict(config)
-        ctx = cls._context(n_ctx, getattr(config, "max_position_embeddings", DEFAULT_CTX))
+        ctx = cls._context(n_ctx, config.max_positions or DEFAULT_CTX)
         decoder = random_model(config, seed, resolve_dtype(dtype), device, max_positions=ctx)
         m = cls(decoder, ctx, max_batch, max_tokens)
         m.load_seconds = time.time() - t0
@@ -86,23 +87,42 @@ class Model:
             self.engine.free_slot(self._slot)
         self._slot = None
         self.cached_ids = []
+        self.last_prefill_forwarded = 0
 
     def prefill(self, tokens) -> torch.Tensor | None:
         """Feeds prompt tokens to the single sequence; float32 logits [vocab] of the last one.
-        (The reference also reuses a cached common prefix, alpacca/model.py:618-625; here the
-        sequence starts anew unless `tokens` continues what is cached.)"""
+
+        As in the reference (alpacca/model.py:610-641): the longest common prefix of `tokens` and
+        what the sequence holds is kept, the cache is truncated to it and only the rest is run; a
+        prompt that is held in full runs its last token again.  `last_prefill_forwarded` counts the
+        tokens that were run.  A model whose cache cannot be truncated starts the sequence anew."""
         tokens = [int(t) for t in tokens]
+        self.last_prefill_forwarded = 0
         if not tokens:
             return None
-        n = len(self.cached_ids)
-        if self._slot is not None and n < len(tokens) and tokens[:n] == self.cached_ids:
-            tokens = tokens[n:]
-        else:
-            self.reset()
+        if len(tokens) > self.n_ctx:
+            raise RuntimeError(f"context window full ({self.n_ctx} tokens)")
+        n = 0
+        if self._slot is not None:
+            top = min(len(tokens), len(self.cached_ids))
+            while n < top and tokens[n] == self.cached_ids[n]:
+                n += 1
+            if n == len(tokens):
+                n = len(tokens) - 1
+            if n != self.n_past:
+                try:
+                    self.engine.truncate(self._slot, n)
+                except ValueError:
+                    n = 0
+                    self.reset()
         if self._slot is None:
             self._slot = self.engine.alloc_slot()
-        logits = self.engine.step([StepEntry(self._slot, tokens, [len(tokens) - 1])])
-        self.cached_ids.extend(tokens)
+        del self.cached_ids[n:]
+        suffix = tokens[n:]
+        logits = self.engine.step([StepEntry(self._slot, suffix, [len(suffix) - 1])])
+        self.engine.wait()       # the reference's prefill returns when the prompt has been evaluated
+        self.cached_ids.extend(suffix)
+        self.last_prefill_forwarded = len(suffix)
         return logits[0]
 
     def forward(self, token: int) -> torch.Tensor:
@@ -152,7 +172,7 @@ def generate(model: Model, prompt_ids, params: SamplerParams | None = None, n_pr
     stop = set(model.decoder.spec.stop_token_ids) | set(stop_token_ids or ())
     sampler = DeviceSampler(params, model.engine.device)
     results = generate_requests(model.engine, sampler, prompts, n_predict, stop, model.max_batch,
-                                bos_token_id=getattr(model.config, "bos_token_id", None), on_token=stream,
+                                bos_token_id=model.config.bos_token if model.config is not None else None, on_token=stream,
                                 decoder=model.decoder_for(sampler))
     return results[0] if single else results
 

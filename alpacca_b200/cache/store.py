@@ -75,6 +75,19 @@ class KVGroup:
                 self.pages.free(pl[i])
                 pl[i] = -1
 
+    def holds_from(self, slot: int, first_pos: int, new_len: int) -> bool:
+        """Whether the pages of positions first_pos .. new_len - 1 are still held (a window gives pages back)."""
+        pl = self.page_lists[slot]
+        return all(pl[i] >= 0 for i in range(first_pos // PAGE_SIZE, min(-(-new_len // PAGE_SIZE), len(pl))))
+
+    def shrink(self, slot: int, new_len: int) -> None:
+        """Gives back the pages that hold only positions from `new_len` on."""
+        pl = self.page_lists[slot]
+        for p in pl[-(-new_len // PAGE_SIZE):]:
+            if p >= 0:
+                self.pages.free(p)
+        del pl[-(-new_len // PAGE_SIZE):]
+
     def close(self, slot: int) -> None:
         for p in self.page_lists.pop(slot):
             if p >= 0:
@@ -176,6 +189,30 @@ class SequenceCache:
     def commit(self, requests) -> None:
         for slot, n_new in requests:
             self.lengths[slot] += n_new
+
+    def truncate(self, slot: int, n: int) -> None:
+        """Keeps only the first `n` tokens of `slot` (the reference's `_truncate_cache`,
+        alpacca/model.py:367-377): the length is set back and the pages that lie wholly behind it
+        are given back; what a kept page holds after position n - 1 is never read.  Refused, with
+        nothing changed, where it cannot be undone: a state of fixed size has no earlier value, and
+        a group with a window may have given back pages that the shorter sequence would read."""
+        if slot not in self.lengths:
+            raise ValueError(f"slot {slot} is not in use")
+        cur = self.lengths[slot]
+        if not 0 <= n <= cur:
+            raise ValueError(f"slot {slot} holds {cur} tokens; it cannot be truncated to {n}")
+        if n == cur:
+            return
+        if self.state_groups:
+            raise ValueError("a sequence whose model keeps a state of fixed size cannot be truncated "
+                             "(the state has no earlier value); free the slot and start again")
+        for g in self.kv_groups:
+            if g.spec.window and not g.holds_from(slot, max(0, n - g.spec.window + 1), n):
+                raise ValueError(f"slot {slot}: pages before position {n} that the window of "
+                                 f"{g.spec.window} needs were already given back")
+        for g in self.kv_groups:
+            g.shrink(slot, n)
+        self.lengths[slot] = n
 
     # -- views -----------------------------------------------------------------
     def table_width(self, group: int, slots) -> int:

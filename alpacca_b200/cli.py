@@ -19,32 +19,39 @@ import sys
 from . import __version__
 
 
-def _add_model_flags(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--ctx", "-c", type=int, default=0, help="context window (tokens)")
-    p.add_argument("--temp", type=float, default=None, help="sampling temperature")
-    p.add_argument("--top-k", type=int, default=None)
-    p.add_argument("--top-p", type=float, default=None)
-    p.add_argument("--repeat-penalty", type=float, default=None)
-    p.add_argument("--seed", "-s", type=int, default=None)
-    p.add_argument("--n-predict", "-n", type=int, default=-1, help="max tokens to generate (-1 = until end)")
-    p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
-                   help="bfloat16 (serving) or float32 (true 32-bit throughout)")
+# One table for the `run` command's options: the parser is built from it, and so are the sampler's
+# options, so a flag and the field it sets cannot drift apart.  Names and short forms are the
+# reference's (alpacca/cli.py:662-671); a sampler flag that is not given leaves the default of
+# `SamplerParams` (alpacca/sample.py:12-19) in place.
+#          flags                    type   sampler field      help
+RUN_FLAGS = (
+    (("--ctx", "-c"),               int,   None,              "context window (tokens)"),
+    (("--temp",),                   float, "temperature",     "sampling temperature"),
+    (("--top-k",),                  int,   "top_k",           None),
+    (("--top-p",),                  float, "top_p",           None),
+    (("--repeat-penalty",),         float, "repeat_penalty",  None),
+    (("--seed", "-s"),              int,   "seed",            None),
+    (("--n-predict", "-n"),         int,   None,              "max tokens to generate (-1 = until end)"),
+)
+RUN_DEFAULTS = {"ctx": 0, "n_predict": -1}      # flags that are no sampler option
 
 
-def _sampler_params(args):
+def _dest(flags) -> str:
+    return flags[0].lstrip("-").replace("-", "_")
+
+
+def add_run_flags(parser: argparse.ArgumentParser) -> None:
+    for flags, kind, field, text in RUN_FLAGS:
+        parser.add_argument(*flags, type=kind, help=text,
+                            default=None if field else RUN_DEFAULTS[_dest(flags)])
+    parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                        help="bfloat16 (serving) or float32 (true 32-bit throughout)")
+
+
+def sampler_params_from(args):
     from .sampling import SamplerParams
-    p = SamplerParams()
-    if args.temp is not None:
-        p.temperature = args.temp
-    if args.top_k is not None:
-        p.top_k = args.top_k
-    if args.top_p is not None:
-        p.top_p = args.top_p
-    if args.repeat_penalty is not None:
-        p.repeat_penalty = args.repeat_penalty
-    if args.seed is not None:
-        p.seed = args.seed
-    return p
+    given = {field: getattr(args, _dest(flags)) for flags, _, field, _ in RUN_FLAGS if field}
+    return SamplerParams(**{k: v for k, v in given.items() if v is not None})
 
 
 def parse_prompts(words) -> list[list[int]]:
@@ -65,7 +72,7 @@ def cmd_run(args) -> int:
     print(f"loading {args.model}...", file=sys.stderr)
     model = Model.load(args.model, n_ctx=args.ctx, dtype=args.dtype, max_batch=max(len(prompts), 1))
     print(model.describe(), file=sys.stderr)
-    results = generate(model, prompts, _sampler_params(args), args.n_predict)
+    results = generate(model, prompts, sampler_params_from(args), args.n_predict)
     for r in results:
         print(" ".join(str(t) for t in r.token_ids), flush=True)
         print(f"[{r.tokens} tokens, {r.tok_per_sec:.1f} tok/s]", file=sys.stderr)
@@ -95,7 +102,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("run", help="generate from a model folder (token ids in, token ids out)")
     p.add_argument("model")
     p.add_argument("prompt", nargs="*")
-    _add_model_flags(p)
+    add_run_flags(p)
     p.set_defaults(func=cmd_run)
 
     p = sub.add_parser("make-random", help="write a model folder with random weights from a config.json")
@@ -113,17 +120,26 @@ def main(argv=None) -> int:
     p.set_defaults(func=cmd_replay)
 
     args = ap.parse_args(argv)
-    if not args.command:
+    return _run_command(ap, args)
+
+
+def _run_command(ap, args) -> int:
+    """Exit codes as the reference's (alpacca/cli.py:751-763): 0, 1 with `alpacca_b200: error: ...`
+    for what the user can mend, 130 when interrupted."""
+    func = getattr(args, "func", None)
+    if func is None:
         ap.print_help()
         return 0
+    code, note = 0, None
     try:
-        return args.func(args)
+        code = func(args)
+    except (RuntimeError, ValueError) as fault:
+        code, note = 1, f"alpacca_b200: error: {fault}"
     except KeyboardInterrupt:
-        print("", file=sys.stderr)
-        return 130
-    except (RuntimeError, ValueError) as e:
-        print(f"alpacca_b200: error: {e}", file=sys.stderr)
-        return 1
+        code, note = 130, ""
+    if note is not None:
+        print(note, file=sys.stderr)
+    return code
 
 
 if __name__ == "__main__":

@@ -75,6 +75,24 @@ class ModelConfig:
         """Faults of the values taken together; empty when the configuration is usable."""
         return []
 
+    # -- what architecture-neutral code asks of any configuration ------------------------
+    # Each architecture answers these from its own keys; nothing outside a configuration class
+    # reads an architecture's key names.
+    @property
+    def max_positions(self) -> int | None:
+        """The longest sequence the model was made for (None: the configuration sets no limit)."""
+        return None
+
+    @property
+    def bos_token(self) -> int | None:
+        """The token an empty prompt is replaced by (None: the model has none)."""
+        return None
+
+    @property
+    def stop_tokens(self) -> tuple[int, ...]:
+        """Tokens that end a sequence."""
+        return ()
+
 
 _SCALARS = {"int": int, "float": (int, float), "bool": bool, "str": str}
 

@@ -62,6 +62,19 @@ class LlamaConfig(ModelConfig):
             return ()
         return tuple(e) if isinstance(e, (list, tuple)) else (int(e),)
 
+    # -- the neutral accessors (config/base.py) ------------------------------------
+    @property
+    def max_positions(self) -> int:
+        return self.max_position_embeddings
+
+    @property
+    def bos_token(self) -> int | None:
+        return self.bos_token_id
+
+    @property
+    def stop_tokens(self) -> tuple[int, ...]:
+        return self.stop_token_ids
+
     def validate(self) -> list[str]:
         bad: list[str] = []
         for name in ("num_hidden_layers", "hidden_size", "num_attention_heads",

@@ -139,18 +139,21 @@ struct Parser {
     }
   }
 
-  // skips any value (used for keys this reader does not know)
-  bool skip() {
+  // skips any value (used for keys this reader does not know); nesting is bounded, so that a
+  // header made of brackets cannot exhaust the stack
+  static constexpr int MAX_DEPTH = 64;
+  bool skip(int depth = 0) {
     ws();
     if (p >= end) return fail("unexpected end");
     if (*p == '"') { std::string s; return string(s); }
     if (*p == '{' || *p == '[') {
+      if (depth >= MAX_DEPTH) return fail("values nested deeper than 64 levels");
       const char open = *p, close = (open == '{') ? '}' : ']';
       ++p;
       if (peek(close)) { ++p; return true; }
       for (;;) {
         if (open == '{') { std::string k; if (!string(k) || !expect(':')) return false; }
-        if (!skip()) return false;
+        if (!skip(depth + 1)) return false;
         if (peek(',')) { ++p; continue; }
         return expect(close);
       }
@@ -250,6 +253,10 @@ ST_API void* st_open(const char* path, char* err, int err_len) {
     long long n = 1;
     for (long long s : e.shape) {
       if (s < 0) return bail("tensor " + e.name + " has a negative size");
+      // the element count times the item size must stay a valid byte count: a product that
+      // wrapped around could equal end - begin and pass the comparison below
+      if (s > 0 && n > (INT64_MAX / isz) / s)
+        return bail("tensor " + e.name + " has a shape whose byte count does not fit 63 bits");
       n *= s;
     }
     if (e.begin < 0 || e.end < e.begin || e.end > data_len)

@@ -73,6 +73,7 @@ class _Shape:
         eng = dec.engine
         dev = eng.device
         self.rows, self.width = rows, width
+        self.max_positions = eng.max_positions      # no sequence of this shape ever grows beyond it
         R = dec.window
         n_groups = len(eng.cache.kv_groups)
         names = ["tokens", "tok_seq", "tok_pos", "cu_q", "kv_len", "slots", "want_rows", "rng_stream", "rng_step",
@@ -113,7 +114,7 @@ class _Shape:
     def context(self) -> StepContext:
         return StepContext(
             n_tokens=self.rows, n_seqs=self.rows, n_want=self.rows, is_decode=True, max_q_len=1,
-            max_kv_len=self.width * PAGE_SIZE, tokens=self.d("tokens"), tok_seq=self.d("tok_seq"),
+            max_kv_len=min(self.width * PAGE_SIZE, self.max_positions), tokens=self.d("tokens"), tok_seq=self.d("tok_seq"),
             tok_pos=self.d("tok_pos"), cu_q=self.d("cu_q"), kv_len=self.d("kv_len"), slots=self.d("slots"),
             want_rows=self.d("want_rows"), block_tables=self.tables_dev(), wants_every_row=True)
 
@@ -175,6 +176,11 @@ class GraphDecoder:
     # -- layout ----------------------------------------------------------------------------
     def _reserve(self, live, steps: int):
         cache = self.engine.cache
+        for slot, _, _ in live:
+            left = cache.max_positions - cache.length(slot)
+            if left < steps:
+                raise CacheFull(f"context window full: slot {slot} holds {cache.length(slot)} tokens, "
+                                f"{steps} more steps exceed the {cache.max_positions} positions of this engine")
         ahead = [(slot, min(max(steps, self.LOOKAHEAD), cache.max_positions - cache.length(slot)))
                  for slot, _, _ in live]
         try:
@@ -239,8 +245,9 @@ class GraphDecoder:
             return self._last_rows
         rows = self._prepare_slow(live, steps, always_mask)
         self._last_slots, self._last_rows = slots, rows
+        # steps that need nothing from the host: room in the pages held and in the context
         self._room = min([len(g.page_lists[s]) * PAGE_SIZE - cache.length(s) for g in cache.kv_groups for s in slots]
-                         + [1 << 30]) - steps
+                         + [cache.max_positions - cache.length(s) for s in slots]) - steps
         return rows
 
     def _prepare_slow(self, live, steps: int, always_mask: bool):

@@ -11,6 +11,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache import CacheFull, SequenceCache
 from ..parts.base import BuildOptions
 from .model import DecoderModel
@@ -24,6 +25,10 @@ class Engine:
         opts: BuildOptions = model.opts
         self.device = torch.device(opts.device)
         self.max_positions = int(max_positions or opts.max_positions)
+        if not 0 < self.max_positions <= opts.max_positions:
+            # tables indexed by position (the rotation's angles) have opts.max_positions rows
+            raise ValueError(f"an engine of {self.max_positions} positions was asked for, the model was built "
+                             f"for {opts.max_positions}")
         n_pages = -(-int(max_tokens) // 64)
         self.max_slots = int(max_slots) if max_slots else max(1, min(n_pages, 1024))
         self.cache = SequenceCache(model.cache_entry_specs(), max_tokens, self.max_slots, self.max_positions,
@@ -41,10 +46,17 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def truncate(self, slot: int, n: int) -> None:
+        """Keeps only the first `n` tokens of the slot's sequence (see `SequenceCache.truncate`)."""
+        self.wait()          # steps in flight still read what is given back
+        self.cache.truncate(slot, n)
+
     def wait(self) -> None:
-        """Returns when every step issued so far has run (steps are issued asynchronously)."""
+        """Returns when every step issued so far has run (steps are issued asynchronously), and
+        raises if a kernel of theirs reported that it gave up (see `ops.check_tc_status`)."""
         if self.device.type == "cuda":
             torch.cuda.current_stream(self.device).synchronize()
+            ops.check_tc_status()
 
     def room_for(self, token_counts) -> bool:
         """Whether new sequences of these lengths fit together into what is free now."""

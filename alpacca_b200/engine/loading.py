@@ -15,6 +15,9 @@ DTYPE_BY_NAME = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": 
                  "fp32": torch.float32, "f32": torch.float32}
 
 
+DEFAULT_MAX_POSITIONS = 4096   # for a configuration that sets no limit (alpacca/model.py:211 has the same default)
+
+
 def resolve_dtype(dtype) -> torch.dtype:
     if isinstance(dtype, torch.dtype):
         if dtype not in (torch.bfloat16, torch.float32):
@@ -32,7 +35,7 @@ def build_model(config: ModelConfig | dict, dtype=torch.bfloat16, device="cuda",
     if isinstance(config, dict):
         config = config_from_dict(config)
     arch = get_architecture(config.architecture)
-    limit = getattr(config, "max_position_embeddings", None) or 4096
+    limit = config.max_positions or DEFAULT_MAX_POSITIONS
     opts = BuildOptions(dtype=resolve_dtype(dtype), device=device,
                         max_positions=min(int(max_positions), limit) if max_positions else limit)
     return DecoderModel(arch.build(config, opts), opts, config)

@@ -3,9 +3,11 @@
 `DecoderSpec` is what an architecture's build function returns: the embedding,
 the layers (each a block of parts), the schedule, the final norm and the head.
 The schedule is a list of runs; a run names the layer it executes and the cache
-entry it uses.  Naming a layer in two runs executes it twice (each run with a
-cache entry of its own); a run whose `reads_entry_of` names an earlier run
-attends to that run's cache and writes none.
+entries it uses.  Naming a layer in two runs executes it twice (each run with
+cache entries of its own); a run whose `reads_entry_of` names an earlier run
+reads that run's cache and writes none.  What a run keeps is the block's to say
+(`cache_specs()`): one entry for each of its parts that keeps keys and values or
+a state, none for a block that keeps nothing.
 
 `DecoderModel` executes a spec for one step: embed the step's tokens, run the
 schedule, norm the wanted rows, project them to logits
@@ -17,7 +19,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..parts.base import BuildOptions, Norm, Part, PositionEncoding
+from ..parts.base import BuildOptions, Norm, Part, PositionEncoding, block_cache_specs
 from ..parts.block import HiddenStream
 from ..parts.embedding import TokenEmbedding, VocabHead
 from ..weights.loader import Fetcher, check_names
@@ -56,9 +58,22 @@ class DecoderSpec:
 class DecoderModel(Part):
     def __init__(self, spec: DecoderSpec, opts: BuildOptions, config=None):
         self.spec, self.opts, self.config = spec, opts, config
-        # cache entry of each run: its own index, or the index of the run it reads
-        self.entry_of_run = [r.reads_entry_of if r.reads_entry_of is not None else i
-                             for i, r in enumerate(spec.schedule)]
+        # the cache entries of each run: its own (one for each spec of its block), or those of the
+        # run it reads
+        self._entry_specs: list = []
+        self.entries_of_run: list[list[int]] = []
+        for i, r in enumerate(spec.schedule):
+            if r.reads_entry_of is not None:
+                theirs = self.entries_of_run[r.reads_entry_of]
+                mine = block_cache_specs(spec.layers[r.layer])
+                if [self._entry_specs[e] for e in theirs] != mine:
+                    raise ValueError(f"run {i} reads the cache of run {r.reads_entry_of}, which keeps "
+                                     "something else than this run's layer would")
+                self.entries_of_run.append(theirs)
+                continue
+            specs = block_cache_specs(spec.layers[r.layer])
+            self.entries_of_run.append(list(range(len(self._entry_specs), len(self._entry_specs) + len(specs))))
+            self._entry_specs.extend(specs)
 
     def children(self):
         s = self.spec
@@ -68,13 +83,13 @@ class DecoderModel(Part):
         return out
 
     def cache_entry_specs(self):
-        """For each run, the cache it owns (None for runs that read another run's)."""
-        out = []
-        for r in self.spec.schedule:
-            mixer = getattr(self.spec.layers[r.layer], "mixer", None)
-            own = r.reads_entry_of is None and mixer is not None
-            out.append(mixer.cache_spec() if own else None)
-        return out
+        """The spec of every cache entry of the schedule, in the order of `entries_of_run`."""
+        return list(self._entry_specs)
+
+    def _views(self, i: int, cache, block_tables):
+        """What run `i`'s block gets as `cache`: its entry's view, a list of views, or None."""
+        views = [cache.entry_view(e, block_tables) for e in self.entries_of_run[i]]
+        return views[0] if len(views) == 1 else (views or None)
 
     def load_weights(self, source, where: str = "") -> int:
         specs = self.param_specs()
@@ -116,7 +131,7 @@ class DecoderModel(Part):
         if s.position is not None:
             s.position.add_to_embeddings(stream.residual, ctx)
         for i, run in enumerate(s.schedule):
-            view = cache.entry_view(self.entry_of_run[i], ctx.block_tables)
+            view = self._views(i, cache, ctx.block_tables)
             stream.next_norm = self._reader_after(i, ctx)
             s.layers[run.layer].forward(stream, ctx, view, write_cache=run.reads_entry_of is None)
         stream.next_norm = None

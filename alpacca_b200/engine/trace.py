@@ -52,9 +52,10 @@ def replay(model_dir, dtype, out_dir, max_tokens: int, lines, out_stream) -> int
             logits = engine.step(entries)
             if logits.shape[0]:
                 arr = logits.to(torch.float32).cpu().contiguous().numpy().astype("<f4", copy=False)
+                engine.wait()          # nothing is written from a step whose kernels gave up
                 arr.tofile(out_dir / f"{step}.f32")
             else:
-                torch.cuda.synchronize()
+                engine.wait()
         for rid in rec.get("end", []):
             rid = str(rid)
             if rid in slots:

@@ -141,12 +141,14 @@ def add_bias(y, bias):
 
 
 def rope_append(qkv, cos, sin, tok_pos, tok_seq, block_table, k_pages, v_pages, n_tokens, H, K, D,
-                n_rot, pairing, write_cache=True):
+                n_rot, pairing, write_cache=True, max_len=None):
     """Rotates q and k of `qkv` [T,(H+2K)D] by position and appends k, v to the pages.
 
     cos/sin: float32 [P, n_rot/2] or None (no rotation); pairing 0 = (2i,2i+1),
     1 = (i, n_rot/2+i).  k_pages/v_pages: [n_pages, K, page, D] of qkv's dtype.
-    The caller guarantees tok_pos < P and that the block table covers tok_pos.
+    `max_len`: the longest sequence of the step after it (tok_pos < max_len); with it the tables'
+    rows and the block table's width are checked here, else the caller guarantees tok_pos < P
+    and that the block table covers tok_pos.
     """
     _cuda(qkv, cos, sin, tok_pos, tok_seq, block_table, k_pages, v_pages)
     _need(qkv.is_contiguous() and qkv.shape[-1] == (H + 2 * K) * D and qkv.numel() >= n_tokens * (H + 2 * K) * D,
@@ -159,7 +161,11 @@ def rope_append(qkv, cos, sin, tok_pos, tok_seq, block_table, k_pages, v_pages, 
         _need(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32
               and cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape
               and cos.shape[-1] == n_rot // 2, "rope tables must be float32 [P, n_rot/2]")
+        _need(max_len is None or max_len <= cos.shape[0],
+              f"rope tables hold {cos.shape[0]} positions, the step reaches position {max_len}")
     page_size = k_pages.shape[2]
+    _need(max_len is None or max_len <= block_table.shape[1] * page_size,
+          f"the block table covers {block_table.shape[1] * page_size} positions, the step reaches {max_len}")
     if write_cache:
         _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype and k_pages.is_contiguous()
               and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (K, page_size, D)
@@ -438,6 +444,7 @@ def attention_mma(qkv, out, cache, ctx, H, K, D, scale, window=0):
     if USE_TCGEN05_ATTENTION and T >= 128 and qkv.shape[0] >= T:
         tc = _lib("attention_tc")
         if tc.ab_attention_prefill_tc_supports(H, K, D):
+            _tc_unchecked["attention_tc"] = True
             tile_seq, tile_q0, n_tiles, _ = _prefill_tiles(ctx, H // K, qkv.device, rows=128)
             _check(tc.ab_attention_prefill_tc(
                 _p(qkv), T, _p(out), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(table), table.shape[1],
@@ -472,6 +479,9 @@ def rope_attention(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, wri
     of the step's tokens over the cache.  Decode steps in bfloat16 do all of it in one kernel; everything else runs the rotation kernel and then `attention`."""
     cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
     T = ctx.n_tokens
+    max_len = getattr(ctx, "max_kv_len", None)
+    if cos is not None and max_len is not None:
+        _need(max_len <= cos.shape[0], f"rope tables hold {cos.shape[0]} positions, the step reaches position {max_len}")
     if (FUSE_ROPE_DECODE and ctx.is_decode and qkv.dtype == torch.bfloat16 and D % 16 == 0 and D <= 256
             and H // K <= 64 and n_rot % 16 == 0):
         _cuda(qkv, out, cache.k, cache.v, cache.block_table)
@@ -482,7 +492,7 @@ def rope_attention(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, wri
               and cache.v.is_contiguous(), "rope_attention: cache pages [n_pages,K,64,D]")
         return _attention_decode(qkv, out, cache, ctx, H, K, D, scale, window, rot, 2 if write_cache else 1)
     rope_append(qkv, cos, sin, ctx.tok_pos, ctx.tok_seq, cache.block_table, cache.k, cache.v, T, H, K, D, n_rot,
-                pairing, write_cache=write_cache)
+                pairing, write_cache=write_cache, max_len=max_len)
     return attention(qkv, out, cache, ctx, H, K, D, scale, window)
 
 
@@ -615,6 +625,7 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
         epi = 1 if out.dtype == torch.float32 else 0
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(), "gemm_tc: bias f32 [N]")
+    _tc_unchecked["gemm_tc"] = True
     if not swap and bn == 256 and slices in (None, 1) and persistent:
         # many rows: the persistent form (tails under the next tile's main loop)
         _check(_lib("gemm_tc").ab_gemm_tc_persistent(_p(x), _p(w), _p(bias), _p(out), n, N, K, out.shape[-1], epi,
@@ -631,6 +642,22 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
     _check(_lib("gemm_tc").ab_gemm_tc(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K,
                                       out.shape[-1], epi, 1 if swap else 0, bn, slices, _stream()), "gemm_tc")
     return out
+
+
+_tc_unchecked = {"gemm_tc": False, "attention_tc": False}   # tcgen05 kernels launched since the last check
+
+
+def check_tc_status() -> None:
+    """Raises `KernelError` if a tcgen05 kernel launched since the last call gave up waiting on a
+    barrier (its output is then unfinished).  Call it where the stream has just been synchronised:
+    it reads one word per library from the device, and nothing when no such kernel ran."""
+    for name, read in (("gemm_tc", gemm_tc_status), ("attention_tc", attention_tc_status)):
+        if _tc_unchecked[name]:
+            _tc_unchecked[name] = False
+            code = read()
+            if code:
+                raise KernelError(f"a tcgen05 kernel of {name} gave up waiting on a barrier (code {code}); "
+                                  "the results of the steps since the last check are not valid")
 
 
 def gemm_tc_status() -> int:

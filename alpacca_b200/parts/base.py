@@ -8,11 +8,14 @@ part knows which model it is in: it never reads a configuration object.
     Mixer         cache_spec() ; forward(h, ctx, cache, write_cache) -> delta
     FeedForward   forward(h, ctx) -> delta
     PositionEncoding  rotation tables for q/k and/or a term added to the embeddings
-    Block         forward(stream, ctx, cache, write_cache): arranges the four above
+    Block         cache_specs() ; forward(stream, ctx, cache, write_cache): arranges the four above
 
 `ctx` is the step's `StepContext` (device index tensors of the packed batch);
 `cache` is what the mixer's `cache_spec()` asked for, for the cache entry that
 the schedule gives this run of the layer: a `KVLayerView` or a `StateLayerView`.
+A block says what its run keeps per sequence with `cache_specs()`, one spec for
+each of its parts that keeps something; with one spec its `forward` gets that
+entry's view, with several a list of views in the same order, with none `None`.
 
 A norm without a kernel of its own (optional; steps of a few rows).  A norm whose
 `deferred()` gives (weight, width, eps) is one factor per row, 1 / rms, times a weight per
@@ -149,6 +152,30 @@ class FeedForward(Part):
 
     def forward(self, h, ctx):
         raise NotImplementedError
+
+
+class Block(Part):
+    """How a layer arranges its parts.  Anything with this `forward` serves as a block; one
+    that has a single `.mixer` and does not define `cache_specs` is read as if it were this
+    default."""
+
+    def cache_specs(self) -> list:
+        """What one run of this block keeps per sequence: a `KVSpec` or `StateSpec` for each part
+        that keeps something, in the order in which `forward` wants their views."""
+        mixer = getattr(self, "mixer", None)
+        spec = mixer.cache_spec() if mixer is not None else None
+        return [spec] if spec is not None else []
+
+    def forward(self, stream, ctx, cache, write_cache: bool = True) -> None:
+        raise NotImplementedError
+
+
+def block_cache_specs(block) -> list:
+    """`block.cache_specs()`, or for a block that does not define it, its `.mixer`'s spec."""
+    own = getattr(block, "cache_specs", None)
+    if own is not None:
+        return [s for s in own() if s is not None]
+    return Block.cache_specs(block)
 
 
 class PositionEncoding(Part):

@@ -14,7 +14,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, OwedNorm, Part
+from .base import Block, FeedForward, Mixer, Norm, OwedNorm
 
 
 @dataclass
@@ -26,7 +26,7 @@ class HiddenStream:
                                        # if its reader accepts an OwedNorm in this step
 
 
-class PreNormBlock(Part):
+class PreNormBlock(Block):
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None, ffn: FeedForward | None):
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
 

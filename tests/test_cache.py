@@ -141,3 +141,63 @@ def test_random_walk_keeps_the_books():
         c.free_slot(s)
     c.check()
     assert c.kv_groups[0].pages.n_held == 0 and c.slots.n_held == 0
+
+
+def test_truncate_gives_back_the_pages_behind_the_new_length():
+    c = make_cache()
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.reserve([(a, 200), (b, 70)])
+    c.commit([(a, 200), (b, 70)])
+    g = c.kv_groups[0]
+    kept = list(g.page_lists[a][:2])
+    assert g.pages.n_held == 4 + 2
+    c.truncate(a, 200)                       # nothing to do
+    assert g.pages.n_held == 6
+    c.truncate(a, 65)                        # positions 0..64: two pages stay, two come back
+    assert c.length(a) == 65 and g.page_lists[a] == kept and g.pages.n_held == 2 + 2
+    c.check()
+    c.truncate(a, 64)                        # a page boundary: the second page holds nothing any more
+    assert g.page_lists[a] == kept[:1] and g.pages.n_held == 1 + 2
+    c.reserve([(a, 10)])                     # and the sequence grows again from there
+    c.commit([(a, 10)])
+    assert c.length(a) == 74 and len(g.page_lists[a]) == 2
+    c.truncate(a, 0)
+    assert c.length(a) == 0 and g.page_lists[a] == [] and g.pages.n_held == 2
+    c.check()
+    with pytest.raises(ValueError, match="cannot be truncated to"):
+        c.truncate(b, 71)
+    with pytest.raises(ValueError, match="cannot be truncated to"):
+        c.truncate(b, -1)
+    with pytest.raises(ValueError, match="not in use"):
+        c.truncate(3, 0)
+    c.free_slot(a)
+    c.free_slot(b)
+    assert g.pages.n_held == 0
+    c.check()
+
+
+def test_truncate_is_refused_where_it_cannot_be_undone():
+    # a state of fixed size has no earlier value
+    c = make_cache(specs=[KVSpec(2, 16), StateSpec((4,))])
+    s = c.alloc_slot()
+    c.reserve([(s, 100)])
+    c.commit([(s, 100)])
+    with pytest.raises(ValueError, match="state of fixed size"):
+        c.truncate(s, 50)
+    c.truncate(s, 100)
+    assert c.length(s) == 100
+    # a window that has given pages back: the shorter sequence would read them
+    c = make_cache(specs=[KVSpec(2, 16, window=70)])
+    s = c.alloc_slot()
+    c.reserve([(s, 250)])
+    c.commit([(s, 250)])
+    c.reserve([(s, 1)])                      # positions before 250 - 70 + 1 = 181 are not needed: pages 0 and 1 go
+    c.commit([(s, 1)])
+    g = c.kv_groups[0]
+    assert g.page_lists[s][:2] == [-1, -1]
+    with pytest.raises(ValueError, match="already given back"):
+        c.truncate(s, 150)                   # would read from position 81, page 1
+    assert c.length(s) == 251
+    c.truncate(s, 200)                       # reads from position 131, page 2: held
+    assert c.length(s) == 200 and len(g.page_lists[s]) == 4
+    c.check()

@@ -109,6 +109,39 @@ def test_reference_style_single_sequence_calls(model_dirs):
     assert "LlamaForCausalLM" in model.describe()
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", None)])
+def test_prefill_keeps_the_longest_common_prefix(model_dirs, dtype, tol):
+    """As tests/smoke.py:974-997 of the reference: only what follows the shared prefix is run, a prompt
+    that is held in full runs its last token again, and a prompt that diverges gives the logits of a
+    fresh sequence (the cache behind the shared prefix was given back)."""
+    from alpacca_b200.api import Model
+    from helpers import check_logits
+    d = model_dirs[("c", dtype)]
+    ids = tiny.prompt_tokens(tiny.TINY_C, 200, 760)
+    base, longer, diverged = ids[:70], ids[:70] + ids[70:150], ids[:70] + ids[160:190]
+    model = Model.load(d, dtype=dtype)
+    pages = model.engine.cache.kv_groups[0].pages
+    model.prefill(base)
+    assert model.last_prefill_forwarded == len(base)
+    got = model.prefill(longer).cpu().numpy()
+    assert model.last_prefill_forwarded == len(longer) - len(base) and model.n_past == len(longer)
+    check_logits(got, plain_model(str(d)).logits(longer)[-1], dtype, "suffix on a cached prefix")
+    again = model.prefill(longer).cpu().numpy()
+    assert model.last_prefill_forwarded == 1 and model.n_past == len(longer)
+    assert np.abs(again - got).max() <= (tol or 4e-2)
+    assert pages.n_held == 3
+    got = model.prefill(diverged).cpu().numpy()
+    assert model.last_prefill_forwarded == len(diverged) - len(base)
+    assert model.cached_ids == diverged and model.n_past == len(diverged) and pages.n_held == 2
+    fresh = Model.load(d, dtype=dtype).prefill(diverged).cpu().numpy()
+    assert np.abs(got - fresh).max() <= (tol or 4e-2)
+    check_logits(got, plain_model(str(d)).logits(diverged)[-1], dtype, "a prompt that diverges")
+    got = model.prefill(ids[100:130]).cpu().numpy()           # nothing shared: from position 0
+    assert model.last_prefill_forwarded == 30 and model.n_past == 30 and pages.n_held == 1
+    check_logits(got, plain_model(str(d)).logits(ids[100:130])[-1], dtype, "nothing shared")
+    model.engine.cache.check()
+
+
 def test_command_line(model_dirs):
     d = model_dirs[("a", "float32")]
     p = tiny.prompt_tokens(tiny.TINY_A, 5, 740)

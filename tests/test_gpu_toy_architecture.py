@@ -1,5 +1,6 @@
 """Another architecture, defined here and nowhere in the package: a mixer with a state of fixed size
-per sequence, a layer that runs twice, a run that reads another run's cache.  It is registered, built,
+per sequence, a layer that runs twice, a run that reads another run's cache, and a layer whose block
+holds two mixers that both keep something (keys and values beside a state).  It is registered, built,
 given random weights, stepped and generated from without a change to the package's files."""
 from dataclasses import dataclass
 
@@ -18,8 +19,8 @@ TOY = {"architectures": ["ToyDecayForCausalLM"], "n_layers": 2, "width": 40, "st
 def define_toy():
     from alpacca_b200.config import ModelConfig, register_architecture, unregister_architecture
     from alpacca_b200.engine.model import DecoderSpec, Run
-    from alpacca_b200.parts import (Attention, Linear, Mixer, PreNormBlock, RMSNorm, RotaryEncoding, StateSpec, SwiGLU,
-                                    TokenEmbedding, VocabHead)
+    from alpacca_b200.parts import (Attention, Block, Linear, Mixer, PreNormBlock, RMSNorm, RotaryEncoding, StateSpec,
+                                    SwiGLU, TokenEmbedding, VocabHead)
     from alpacca_b200.weights import ParamSpec
 
     @dataclass(frozen=True)
@@ -35,7 +36,15 @@ def define_toy():
         eps: float = 1e-5
         positions: int = 256
         eos_token_id: int = 0
-        max_position_embeddings: int = 256
+
+        # what architecture-neutral code asks of a configuration, answered from this one's own keys
+        @property
+        def max_positions(self):
+            return self.positions
+
+        @property
+        def stop_tokens(self):
+            return (self.eos_token_id,)
 
     class DecayMixer(Mixer):
         """s_t = sigmoid(a) * s_{t-1} + W_in h_t;  y_t = W_out s_t.  The state s lives per sequence."""
@@ -71,6 +80,24 @@ def define_toy():
                 at += n
             return self.w_out.forward(ys.to(h.dtype), n_rows=ctx.n_tokens)
 
+    class HybridBlock(Block):
+        """x += Attention(Norm1(x)) + Decay(Norm1(x)); x += FeedForward(Norm2(x)): two mixers in one
+        layer, each with a cache entry of its own (keys and values; a state)."""
+
+        def __init__(self, norm1, attention, decay, norm2, ffn):
+            self.norm1, self.attention, self.decay, self.norm2, self.ffn = norm1, attention, decay, norm2, ffn
+
+        def cache_specs(self):
+            return [self.attention.cache_spec(), self.decay.cache_spec()]
+
+        def forward(self, stream, ctx, cache, write_cache=True):
+            kv, state = cache
+            h = self.norm1.forward(stream.residual, stream.delta)
+            a = self.attention.forward(h, ctx, kv, write_cache)
+            d = self.decay.forward(h, ctx, state, write_cache)
+            h = self.norm2.forward(stream.residual, (a.float() + d.float()).to(a.dtype))
+            stream.delta = self.ffn.forward(h, ctx)
+
     unregister_architecture("ToyDecayForCausalLM")
 
     @register_architecture("ToyDecayForCausalLM", ToyConfig)
@@ -84,9 +111,14 @@ def define_toy():
             PreNormBlock(RMSNorm(opts, E, cfg.eps, "l1.n1"),
                          Attention(opts, E, cfg.heads, cfg.kv_heads, cfg.head_dim, rope, "l1.attn"),
                          RMSNorm(opts, E, cfg.eps, "l1.n2"), SwiGLU(opts, E, cfg.inner, "l1.ffn")),
+            HybridBlock(RMSNorm(opts, E, cfg.eps, "l2.n1"),
+                        Attention(opts, E, cfg.heads, cfg.kv_heads, cfg.head_dim, rope, "l2.attn"),
+                        DecayMixer(opts, E, cfg.state, "l2.mix"),
+                        RMSNorm(opts, E, cfg.eps, "l2.n2"), SwiGLU(opts, E, cfg.inner, "l2.ffn")),
         ]
-        # layer 0 runs twice (two states), layer 1 runs twice and its second run reads the first one's keys
-        schedule = [Run(0), Run(1), Run(0), Run(1, reads_entry_of=1)]
+        # layer 0 runs twice (two states), layer 1 runs twice and its second run reads the first one's
+        # keys, layer 2 keeps keys and a state at once
+        schedule = [Run(0), Run(1), Run(0), Run(1, reads_entry_of=1), Run(2)]
         return DecoderSpec(embedding=emb, layers=layers, final_norm=RMSNorm(opts, E, cfg.eps, "norm"),
                            head=VocabHead(opts, cfg.vocab, E, "head", tied_to=emb), schedule=schedule,
                            stop_token_ids=(cfg.eos_token_id,), vocab_size=cfg.vocab)
@@ -106,30 +138,40 @@ def plain_toy(cfg, w, tokens):
         a = plain.swiglu(plain.linear(h, w[p + ".ffn.gate_proj.weight"]), plain.linear(h, w[p + ".ffn.up_proj.weight"]))
         return x + plain.linear(a, w[p + ".ffn.down_proj.weight"])
 
-    def decay_layer(x):
-        h = plain.rmsnorm(x, w["l0.n1.weight"], cfg["eps"])
-        u = plain.linear(h, w["l0.mix.in_proj.weight"])
-        a = 1 / (1 + np.exp(-w["l0.mix.decay"]))
+    def decay(h, p):
+        u = plain.linear(h, w[p + ".mix.in_proj.weight"])
+        a = 1 / (1 + np.exp(-w[p + ".mix.decay"]))
         s, ys = np.zeros(cfg["state"]), []
         for t in range(T):
             s = a * s + u[t]
             ys.append(s)
-        return ffn(x + plain.linear(np.stack(ys), w["l0.mix.out_proj.weight"]), "l0")
+        return plain.linear(np.stack(ys), w[p + ".mix.out_proj.weight"])
 
-    def attn_layer(x, kv=None):
-        h = plain.rmsnorm(x, w["l1.n1.weight"], cfg["eps"])
-        q = plain.rope(plain.linear(h, w["l1.attn.q_proj.weight"]), pos, H, D, D, inv, "neox")
+    def attend(h, p, kv=None):
+        q = plain.rope(plain.linear(h, w[p + ".attn.q_proj.weight"]), pos, H, D, D, inv, "neox")
         if kv is None:
-            k = plain.rope(plain.linear(h, w["l1.attn.k_proj.weight"]), pos, K, D, D, inv, "neox")
-            v = plain.linear(h, w["l1.attn.v_proj.weight"]).reshape(T, K, D)
+            k = plain.rope(plain.linear(h, w[p + ".attn.k_proj.weight"]), pos, K, D, D, inv, "neox")
+            v = plain.linear(h, w[p + ".attn.v_proj.weight"]).reshape(T, K, D)
             kv = (k, v)
         a = plain.attention(q, kv[0], kv[1]).reshape(T, H * D)
-        return ffn(x + plain.linear(a, w["l1.attn.o_proj.weight"]), "l1"), kv
+        return plain.linear(a, w[p + ".attn.o_proj.weight"]), kv
+
+    def decay_layer(x):
+        return ffn(x + decay(plain.rmsnorm(x, w["l0.n1.weight"], cfg["eps"]), "l0"), "l0")
+
+    def attn_layer(x, kv=None):
+        a, kv = attend(plain.rmsnorm(x, w["l1.n1.weight"], cfg["eps"]), "l1", kv)
+        return ffn(x + a, "l1"), kv
+
+    def hybrid_layer(x):
+        h = plain.rmsnorm(x, w["l2.n1.weight"], cfg["eps"])
+        return ffn(x + attend(h, "l2")[0] + decay(h, "l2"), "l2")
 
     x = decay_layer(x)
     x, kv = attn_layer(x)
     x = decay_layer(x)
     x, _ = attn_layer(x, kv)
+    x = hybrid_layer(x)
     return plain.linear(plain.rmsnorm(x, w["norm.weight"], cfg["eps"]), w["emb.weight"])
 
 
@@ -149,8 +191,9 @@ def test_registered_built_and_loaded(toy_dir):
     assert "ToyDecayForCausalLM" in registered_architectures()
     model = load_model_dir(toy_dir, dtype="float32")
     specs = model.cache_entry_specs()
-    assert [type(s).__name__ if s else None for s in specs] == ["StateSpec", "KVSpec", "StateSpec", None]
-    assert model.entry_of_run == [0, 1, 2, 1] and not model.all_capturable()
+    assert [type(s).__name__ for s in specs] == ["StateSpec", "KVSpec", "StateSpec", "KVSpec", "StateSpec"]
+    # the fourth run reads the second run's entry; the last run's block keeps two things
+    assert model.entries_of_run == [[0], [1], [2], [1], [3, 4]] and not model.all_capturable()
     names = {s.name for s in model.param_specs() if not s.absent}
     assert set(plain.read_safetensors(toy_dir / "model.safetensors")) == names
 
@@ -161,7 +204,8 @@ def test_stepped_whole_one_by_one_and_in_batches(toy_dir, dtype, rel):
     from alpacca_b200.engine.loading import load_model_dir
     cfg, w = plain.read_model_dir(toy_dir)
     eng = Engine(load_model_dir(toy_dir, dtype=dtype), max_tokens=64 * 8, max_slots=3)
-    assert len(eng.cache.state_groups) == 1 and eng.cache.state_groups[0].state.shape[:2] == (2, 3)
+    assert len(eng.cache.state_groups) == 1 and eng.cache.state_groups[0].state.shape[:2] == (3, 3)
+    assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].n_entries == 2
     rng = np.random.default_rng(0)
     seqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (70, 9, 33)]
     want = [plain_toy(cfg, w, s) for s in seqs]

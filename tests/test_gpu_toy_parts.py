@@ -41,7 +41,15 @@ def define_toy():
         positions: int = 128
         window: int = 16
         eos_token_id: int = 0
-        max_position_embeddings: int = 128
+
+        # what architecture-neutral code asks of a configuration, answered from this one's own keys
+        @property
+        def max_positions(self):
+            return self.positions
+
+        @property
+        def stop_tokens(self):
+            return (self.eos_token_id,)
 
     class LearnedPositions(PositionEncoding):
         """x_t += table[position of t]; nothing is rotated."""

@@ -51,6 +51,14 @@ def test_broken_files_are_refused(tmp_path):
     h = json.dumps({"w": {"dtype": "F8_E4M3", "shape": [2], "data_offsets": [0, 2]}}).encode()
     with pytest.raises(SafetensorsError, match="unsupported dtype"):
         SafetensorsFile(_raw(tmp_path, h, b"\0" * 2))
+    # a shape whose byte count wraps around 2^64 to exactly the bytes that are there
+    h = json.dumps({"w": {"dtype": "F32", "shape": [2 ** 31, 2 ** 31, 4], "data_offsets": [0, 0]}}).encode()
+    with pytest.raises(SafetensorsError, match="does not fit 63 bits"):
+        SafetensorsFile(_raw(tmp_path, h, b""))
+    # an unknown key whose value is nested a hundred thousand levels deep
+    deep = b'{"__metadata__":{},"x":{"dtype":"F32","shape":[],"data_offsets":[0,4],"extra":' + b"[" * 100000 + b"]" * 100000 + b"}}"
+    with pytest.raises(SafetensorsError, match="nested deeper"):
+        SafetensorsFile(_raw(tmp_path, deep, b"\0" * 4))
     with pytest.raises(SafetensorsError, match="no model.safetensors"):
         FolderSource(tmp_path / "nowhere")
 
