@@ -96,6 +96,7 @@ class _Shape:
         self.history = torch.zeros((dec.history_len, rows), dtype=torch.int32, device=dev)
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.graph = None
+        self.logits = None      # set at capture: the logits of the last replay (after the repeat penalty)
 
     def d(self, name):
         o, n = self.sect[name]
@@ -144,6 +145,7 @@ class GraphDecoder:
     def _body(self, sh: _Shape):
         eng, p = self.engine, self.sampler.params
         logits = eng.model.forward(sh.context(), eng.cache)
+        sh.logits = logits      # float32 [rows, vocab] in the graph's own memory: every replay writes it anew
         o, n = sh.recent_sect
         recent = sh.dev[o:o + n].view(sh.rows, self.window) if self.window else None
         if recent is not None:

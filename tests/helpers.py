@@ -8,15 +8,31 @@ import numpy as np
 import plain_llama as plain
 import tiny
 
-CONFIGS = {"a": tiny.TINY_A, "b": tiny.TINY_B, "c": tiny.TINY_C, "d": tiny.TINY_D, "e": tiny.TINY_E}
+CONFIGS = {"a": tiny.TINY_A, "b": tiny.TINY_B, "c": tiny.TINY_C, "d": tiny.TINY_D, "e": tiny.TINY_E,
+           # the same configurations with weights N(0, 0.1) (see conftest.model_dirs)
+           "B": tiny.TINY_B, "C": tiny.TINY_C, "D": tiny.TINY_D, "E": tiny.TINY_E}
 
-# Largest allowed |engine - plain| on logits.  The plain implementation is float64 on the stored
-# weights.  float32: rounding of float32 sums over at most a few hundred terms, logits of order 1.
-# bfloat16: activations are rounded to 8 bits of mantissa between the kernels (relative 2^-9 each,
-# some dozens of roundings along the path, logits of order 1).
-LOGIT_TOL = {"float32": 5e-5, "bfloat16": 6e-2}
-# mean |difference| must be far below the maximum allowed
-LOGIT_MEAN_TOL = {"float32": 1e-5, "bfloat16": 1.2e-2}
+# Allowed |engine - plain| on logits.  The plain implementation is float64 on the stored weights.
+# float32: absolute; rounding of float32 sums over at most a few hundred terms, logits of order 1.
+# bfloat16: a share of the spread (standard deviation) of the plain logits that are compared,
+# since activations are rounded to 8 bits of mantissa between the kernels and the error grows with
+# the values.  The shares are three times the largest error measured over all tests of the suite
+# (conftest's error report).  For scale: with the rotation's pairing swapped, or the frequency
+# scaling left out, the logits of the N(0, 0.1) models move by 0.3 to 0.7 of their spread.
+LOGIT_TOL = {"float32": 5e-5}
+LOGIT_MEAN_TOL = {"float32": 1e-5}
+BF16_MAX_SHARE = 0.10
+BF16_MEAN_SHARE = 0.02
+
+SEEN: dict = {}     # (label without its numbers, dtype) -> (largest max/std, largest mean/std, count)
+
+
+def logit_tolerances(want, dtype: str):
+    """(largest, mean) allowed |difference| against the plain logits `want`."""
+    if dtype == "bfloat16":
+        spread = float(np.asarray(want, np.float64).std())
+        return BF16_MAX_SHARE * spread, BF16_MEAN_SHARE * spread
+    return LOGIT_TOL[dtype], LOGIT_MEAN_TOL[dtype]
 
 
 @functools.lru_cache(maxsize=None)
@@ -41,9 +57,14 @@ def check_logits(got, want, dtype: str, what: str = "") -> None:
     assert np.isfinite(got).all(), f"{what}: logits are not finite"
     diff = np.abs(got - want)
     worst = np.unravel_index(np.argmax(diff), diff.shape)
-    assert diff.max() <= LOGIT_TOL[dtype], (f"{what}: max |diff| {diff.max():.3e} at {worst} "
-                                            f"(allowed {LOGIT_TOL[dtype]:.1e}, mean {diff.mean():.3e})")
-    assert diff.mean() <= LOGIT_MEAN_TOL[dtype], f"{what}: mean |diff| {diff.mean():.3e}"
+    tol, mean_tol = logit_tolerances(want, dtype)
+    spread = max(float(want.std()), 1e-30)
+    key = ("".join(c for c in what if not c.isdigit()), dtype)
+    old = SEEN.get(key, (0.0, 0.0, 0))
+    SEEN[key] = (max(old[0], diff.max() / spread), max(old[1], diff.mean() / spread), old[2] + 1)
+    assert diff.max() <= tol, (f"{what}: max |diff| {diff.max():.3e} at {worst} (allowed {tol:.2e}, "
+                               f"mean {diff.mean():.3e}, spread of the logits {spread:.3e})")
+    assert diff.mean() <= mean_tol, f"{what}: mean |diff| {diff.mean():.3e} (allowed {mean_tol:.2e})"
 
 
 def load_part(part, seed=0, dtype="float32", std=0.3):

@@ -10,7 +10,7 @@ from helpers import CONFIGS, check_logits, plain_logits
 pytestmark = pytest.mark.gpu
 
 DTYPES = ("float32", "bfloat16")
-NAMES = ("a", "b", "c", "d", "e")
+NAMES = ("a", "b", "c", "d", "e", "B", "C", "D", "E")     # upper case: weights N(0, 0.1), sharp attention
 
 
 def make_engine(model_dir, dtype, max_tokens=64 * 24, max_slots=8, max_positions=None):
@@ -22,7 +22,7 @@ def make_engine(model_dir, dtype, max_tokens=64 * 24, max_slots=8, max_positions
 
 def lengths_for(name):
     top = CONFIGS[name]["max_position_embeddings"]
-    return [n for n in (1, 9, 33, 70, 64, 65, 127, 128, 200, 331) if n <= top]
+    return [n for n in (1, 9, 33, 70, 63, 64, 65, 127, 128, 200, 331, 600) if n <= top]     # 600: ten pages
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -110,10 +110,10 @@ def test_unequal_batches_one_after_another(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(model_dirs, dtype):
+@pytest.mark.parametrize("name", ["c", "C"])
+def test_long_decoding(model_dirs, name, dtype):
     """A short prompt and then hundreds of single-token steps across several pages."""
     from alpacca_b200.engine import StepEntry
-    name = "c"
     d = model_dirs[(name, dtype)]
     eng = make_engine(d, dtype, max_tokens=64 * 6)
     toks = tiny.prompt_tokens(CONFIGS[name], 330, 400)
@@ -150,11 +150,12 @@ def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_padding_and_batch_do_not_change_a_result(model_dirs, dtype):
+@pytest.mark.parametrize("name", ["b", "B"])
+def test_padding_and_batch_do_not_change_a_result(model_dirs, name, dtype):
     """The same request alone, in a batch, and cut into uneven steps gives the same logits
     (equal up to rounding; in 32-bit the kernels make them equal to the last bit)."""
     from alpacca_b200.engine import StepEntry
-    name = "b"
+    from helpers import logit_tolerances
     d = model_dirs[(name, dtype)]
     eng = make_engine(d, dtype)
     toks = tiny.prompt_tokens(CONFIGS[name], 75, 600)
@@ -172,13 +173,14 @@ def test_padding_and_batch_do_not_change_a_result(model_dirs, dtype):
     cut = np.concatenate(cut)
     if dtype == "float32":
         assert np.array_equal(alone, both), "a batch neighbour changed 32-bit logits"
-        assert np.abs(alone - cut).max() <= 2e-6
+        assert np.abs(alone - cut).max() <= 2e-6 * max(1.0, np.abs(alone).max())
     else:
-        assert np.abs(alone - both).max() <= 2e-2 and np.abs(alone - cut).max() <= 4e-2
+        tol = logit_tolerances(alone, dtype)[0]
+        assert np.abs(alone - both).max() <= tol and np.abs(alone - cut).max() <= tol
     check_logits(cut, plain_logits(d, toks), dtype, "cut into steps")
 
 
-@pytest.mark.parametrize("name", ["b", "e"])
+@pytest.mark.parametrize("name", ["b", "e", "B", "E"])
 def test_norms_inside_the_products_change_no_result(model_dirs, name, monkeypatch):
     """Steps of a few rows run the RMS norms inside the products before and after them.  With that
     switched off the same logits come out, within bfloat16 rounding, from more kernels."""
@@ -202,4 +204,5 @@ def test_norms_inside_the_products_change_no_result(model_dirs, name, monkeypatc
             for b in range(len(seqs)):
                 check_logits(got[i][b], want[b][len(seqs[b]) - p], "bfloat16", f"{name} defer={defer} step {i} seq {b}")
     assert runs[True][1] < runs[False][1], "the norms still ran as kernels of their own"
-    assert np.abs(runs[True][0] - runs[False][0]).max() <= 4e-2
+    from helpers import logit_tolerances
+    assert np.abs(runs[True][0] - runs[False][0]).max() <= logit_tolerances(runs[False][0], "bfloat16")[0]

@@ -14,13 +14,15 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def margin_ok(model_dir, prompt, tokens, tol):
-    """Every generated token is the plain model's argmax for the same prefix, or within `tol` of it."""
+def margin_ok(model_dir, prompt, tokens, dtype):
+    """Every generated token is the plain model's argmax for the same prefix, or as close to it as two
+    logits can be swapped by the engine's allowed error (each may be off by the tolerance)."""
+    from helpers import logit_tolerances
     pm = plain_model(str(model_dir))
     seq = list(prompt)
     for t in tokens:
         row = pm.logits(seq)[-1]
-        if row[t] < row.max() - tol:
+        if row[t] < row.max() - 2 * logit_tolerances(row, dtype)[0]:
             return False
         seq.append(t)
     return True
@@ -28,7 +30,7 @@ def margin_ok(model_dir, prompt, tokens, tol):
 
 @pytest.mark.parametrize("graphs", [True, False])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "B"])
 def test_greedy_generation_of_an_unequal_batch(model_dirs, name, dtype, graphs):
     from alpacca_b200.api import Model, generate
     from alpacca_b200.sampling import SamplerParams
@@ -46,7 +48,7 @@ def test_greedy_generation_of_an_unequal_batch(model_dirs, name, dtype, graphs):
         if dtype == "float32":
             kept = [t for t in want if t not in stops]
             assert r.token_ids == kept and r.tokens == len(want)
-        assert margin_ok(d, p, r.token_ids, 1e-4 if dtype == "float32" else 0.08)
+        assert margin_ok(d, p, r.token_ids, dtype)
         assert r.finish_reason in ("length", "stop") and r.prompt_tokens == len(p)
     one = generate(model, prompts[1], SamplerParams.greedy(), n_predict=8)
     assert one.token_ids == res[1].token_ids, "a request alone and in a batch must give the same tokens"

@@ -1,0 +1,158 @@
+"""The engine at the layer widths of real models, in 32-bit and in bfloat16, against the plain
+implementation: two layers of the Llama-3.2-1B sizes (of its sixteen) and two of the Llama-3.1-8B
+sizes (of its thirty-two).
+
+Only these widths reach, through the engine, the persistent tcgen05 gate|up product (1,024 rows and
+more), the tcgen05 prefill attention at a real group size, the products whose norm is finished by
+the product after it (and those where it is not), the 16-warp form of the down projection, and a
+head and sampler over a vocabulary of 128,256.  One prompt of more than 1,100 tokens whole, its last
+8 tokens one by one, and a batch of three unequal prompts; logits are asked for at a handful of
+places so that the plain vocabulary product stays cheap.  The rule is the reference's
+(tests/smoke.py:931-972): every way of running the model gives the same logits.
+"""
+import numpy as np
+import pytest
+
+import plain_llama as plain
+import tiny
+from helpers import check_logits
+
+pytestmark = pytest.mark.gpu
+
+WIDTHS_1B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 128256, "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_pairing": "neox",
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True, "hidden_act": "silu", "bos_token_id": 128000, "eos_token_id": 128001,
+}
+# the 8B layer sizes; the vocabulary is cut to 16,000 (the head of 128,256 rows is covered above)
+WIDTHS_8B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+    "vocab_size": 16000, "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_pairing": "neox",
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+SHAPES = {"1b": (WIDTHS_1B, 21, 1130), "8b": (WIDTHS_8B, 22, 1060)}
+
+
+class PlainAtPlaces:
+    """The plain model's logits at chosen places of a sequence (the hidden states of a sequence are
+    computed once and kept)."""
+
+    def __init__(self, model_dir):
+        self.pm = plain.PlainLlama.from_dir(model_dir)
+        self.hidden = {}
+
+    def logits(self, tokens, places):
+        key = tuple(tokens)
+        if key not in self.hidden:
+            self.hidden[key] = self.pm.hidden(list(tokens))
+        pm = self.pm
+        x = plain.rmsnorm(self.hidden[key][list(places)], pm.w["model.norm.weight"], pm.eps)
+        head = pm.w["model.embed_tokens.weight"] if pm.tied else pm.w["lm_head.weight"]
+        return plain.linear(x, head)
+
+
+@pytest.fixture(scope="module", params=["1b", "8b"])
+def wide(request, tmp_path_factory):
+    """(name, config, {dtype: folder}, {dtype: PlainAtPlaces}, long prompt length).  Weights N(0, 0.02)
+    as the benchmark configurations prescribe; at these widths that already gives logits of order 1."""
+    import torch
+    from alpacca_b200.engine.loading import write_random_model_dir
+    cfg, seed, long_len = SHAPES[request.param]
+    root = tmp_path_factory.mktemp(f"wide_{request.param}")
+    dirs = {dt: write_random_model_dir(root / dt, cfg, seed, dtype=getattr(torch, dt)) for dt in ("float32", "bfloat16")}
+    plains = {}
+    yield request.param, cfg, dirs, plains, long_len
+
+
+# float32 at these widths: sums of 2,048 to 14,336 terms, which the engine's float32 products add in
+# one ascending chain per output and the plain implementation in float64; logits of order 1
+FLOAT32_TOL = 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_then_one_by_one_then_a_batch(wide, dtype):
+    from alpacca_b200 import ops
+    from alpacca_b200.engine import Engine, StepEntry
+    from alpacca_b200.engine.loading import load_model_dir
+    name, cfg, dirs, plains, long_len = wide
+    d = dirs[dtype]
+    if dtype not in plains:
+        plains[dtype] = PlainAtPlaces(d)
+    pl = plains[dtype]
+    eng = Engine(load_model_dir(d, dtype=dtype, device="cuda", max_positions=2048), max_tokens=64 * 48, max_slots=4)
+
+    def check(got, want, what):
+        if dtype == "bfloat16":
+            check_logits(got, want, dtype, f"{name} widths, {what}")
+            return
+        diff = np.abs(np.asarray(got, np.float64) - want)
+        assert got.shape == want.shape and np.isfinite(got).all()
+        worst[0] = max(worst[0], float(diff.max()))
+        assert diff.max() <= FLOAT32_TOL, f"{name} widths, {what}: max |diff| {diff.max():.3e} (logit spread {want.std():.2f})"
+
+    worst = [0.0]
+
+    # 1. one long prompt whole: more than 1,024 rows in every product
+    toks = tiny.prompt_tokens(cfg, long_len, 3000)
+    places = [0, 1, 63, 64, 500, 1023, 1024, long_len - 9, long_len - 1]
+    slot = eng.alloc_slot()
+    before = ops.launches
+    got = eng.step([StepEntry(slot, toks[:long_len - 8], [p for p in places if p < long_len - 8])])
+    eng.wait()
+    assert ops.launches > before
+    check(got.cpu().numpy(), pl.logits(toks, [p for p in places if p < long_len - 8]), "long prompt whole")
+    # 2. its last 8 tokens one by one, on the cache that the long step left
+    for p in range(long_len - 8, long_len):
+        got = eng.step([StepEntry(slot, [toks[p]], [0])]).cpu().numpy()
+        check(got, pl.logits(toks, [p]), f"token {p} fed alone")
+    eng.free_slot(slot)
+    # 3. three unequal prompts in one step (slots and pages used again), then two steps of one token each
+    seqs = [tiny.prompt_tokens(cfg, n, 3100 + i) for i, n in enumerate((300, 131, 40))]
+    slots = [eng.alloc_slot() for _ in seqs]
+    heads = [len(s) - 2 for s in seqs]
+    got = eng.step([StepEntry(sl, s[:h], [0, h - 1]) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+    for i, (s, h) in enumerate(zip(seqs, heads)):
+        check(got[2 * i:2 * i + 2], pl.logits(s, [0, h - 1]), f"batch of three, prompt {i}")
+    for k in range(2):
+        got = eng.step([StepEntry(sl, [s[h + k]], [0]) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+        for i, (s, h) in enumerate(zip(seqs, heads)):
+            check(got[i:i + 1], pl.logits(s, [h + k]), f"batch of three, decode step {k} of sequence {i}")
+    for sl in slots:
+        eng.free_slot(sl)
+    eng.cache.check()
+    assert ops.gemm_tc_status() == 0 and ops.attention_tc_status() == 0
+    if dtype == "float32":
+        print(f"{name} widths, float32: largest |engine - plain| {worst[0]:.3e}")
+
+
+def test_generation_in_bfloat16_at_the_1b_widths(wide):
+    """Greedy generation of eight unequal prompts through the entry point, replayed from graphs: the
+    sampler and the head over the full vocabulary inside a graph; every token is the plain model's
+    choice within the tolerance."""
+    from alpacca_b200.api import Model, generate
+    from alpacca_b200.sampling import SamplerParams
+    from helpers import logit_tolerances
+    name, cfg, dirs, plains, _ = wide
+    if name != "1b":
+        pytest.skip("once, at the vocabulary of 128,256")
+    d = dirs["bfloat16"]
+    if "bfloat16" not in plains:
+        plains["bfloat16"] = PlainAtPlaces(d)
+    pl = plains["bfloat16"]
+    prompts = [tiny.prompt_tokens(cfg, n, 3200 + i) for i, n in enumerate((5, 64, 17, 100, 1, 33, 65, 9))]
+    model = Model.load(d, dtype="bfloat16", n_ctx=256, max_batch=8)
+    res = generate(model, prompts, SamplerParams.greedy(), n_predict=4, stop_token_ids=[])
+    assert model.use_graphs
+    for b in (0, 3, 4, 6):
+        seq = list(prompts[b]) + res[b].token_ids
+        rows = pl.logits(seq[:-1], list(range(len(prompts[b]) - 1, len(seq) - 1)))
+        for row, t in zip(rows, res[b].token_ids):
+            assert row[t] >= row.max() - 2 * logit_tolerances(row, "bfloat16")[0], (b, t, int(np.argmax(row)))

@@ -5,7 +5,10 @@ Such a caller cannot allocate device memory when it calls (its memory was handed
 or it sits in a loop that must not synchronise the device), so the scratch memory of the split over
 key chunks lives inside the library.  This test checks that the entry point gives what the package's
 own entry point gives when that one is handed scratch tensors, twice in a row (the second call finds
-the scratch as the first left it), and that it refuses problems beyond its stated limit.
+the scratch as the first left it), that both agree with a float64 restatement of the attention on the
+same inputs (with and without a window, with a row of the batch that holds no sequence), that a call
+leaves the device's free memory as it found it, and that it refuses problems beyond either of its
+stated limits.
 
 The file sorts last on purpose: a run that stops at the first failure has then run everything else.
 """
@@ -38,6 +41,27 @@ def _p(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
+def _plain_attention(qkv, k, v, table, seq, lens, H, K, D, window):
+    """softmax(q . k / sqrt(D)) v over each sequence's keys (the last `window` of them), float64;
+    a row whose `seq` is -1 holds no sequence and is left at zero."""
+    qkv, k, v = qkv.double().cpu(), k.double().cpu(), v.double().cpu()
+    table, seq, lens = table.cpu(), seq.tolist(), lens.tolist()
+    out = torch.zeros(len(seq), H * D, dtype=torch.float64)
+    G = H // K
+    for row, b in enumerate(seq):
+        if b < 0:
+            continue
+        n = lens[b]
+        pages = table[b, :-(-n // 64)].long()
+        lo = max(0, n - window) if window else 0
+        for h in range(H):
+            keys = k[pages, h // G].reshape(-1, D)[lo:n]
+            vals = v[pages, h // G].reshape(-1, D)[lo:n]
+            p = torch.softmax(keys @ qkv[row, h * D:(h + 1) * D] * D ** -0.5, dim=0)
+            out[row, h * D:(h + 1) * D] = p @ vals
+    return out
+
+
 def test_no_alloc_entry_point_matches_the_package_s_own():
     from alpacca_b200.ops import build
     lib = build.load("attention_mma")
@@ -45,8 +69,12 @@ def test_no_alloc_entry_point_matches_the_package_s_own():
     H, K, D = 8, 2, 64
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     ppc = 2          # pages per chunk: more than 8 chunks, which are merged through the scratch memory
-    for call, lengths in enumerate(([1500, 70, 2048, 1025], [900, 2047, 33, 1300])):   # several chunks each
+    cases = (([1500, 70, 2048, 1025], 0, None), ([900, 2047, 33, 1300], 0, None),
+             ([1100, 2040, 64, 700], 300, 2))        # the last: a window of 300 keys, and row 2 holds no sequence
+    for call, (lengths, window, empty_row) in enumerate(cases):   # several chunks each
         qkv, k, v, table, seq, lens = _setup(lengths, H, K, D, seed=call)
+        if empty_row is not None:
+            seq[empty_row] = -1
         B, W = table.shape
         n_chunks = -(-W // ppc)
         assert n_chunks > 8, "the case must need the scratch memory"
@@ -57,24 +85,34 @@ def test_no_alloc_entry_point_matches_the_package_s_own():
         arrivals = torch.zeros(B * K, dtype=torch.int32, device="cuda")
         rc = lib.ab_attention_decode_bf16(_p(qkv), qkv.shape[1], _p(want), _p(part_o), _p(part_ml), _p(arrivals),
                                           _p(k), _p(v), _p(table), W, _p(seq), _p(lens), B, H, K, D,
-                                          ctypes.c_float(D ** -0.5), 0, ppc, n_chunks, 0, stream)
+                                          ctypes.c_float(D ** -0.5), window, ppc, n_chunks, 0, stream)
         assert rc == 0
+        # what the attention is, restated in float64 on the same inputs
+        plain = _plain_attention(qkv, k, v, table, seq, lens, H, K, D, window).cuda()
+        assert (want.double() - plain).abs().max().item() <= 1.6e-2
         # few chunks, merged inside a cluster without scratch: the same result by another route
         few = torch.zeros(B, H * D, dtype=torch.bfloat16, device="cuda")
         rc = lib.ab_attention_decode_bf16(_p(qkv), qkv.shape[1], _p(few), None, None, None, _p(k), _p(v), _p(table),
-                                          W, _p(seq), _p(lens), B, H, K, D, ctypes.c_float(D ** -0.5), 0, 8,
+                                          W, _p(seq), _p(lens), B, H, K, D, ctypes.c_float(D ** -0.5), window, 8,
                                           -(-W // 8), 0, stream)
         assert rc == 0
         assert (few.float() - want.float()).abs().max().item() <= 1.6e-2
         # the entry point that allocates nothing: inputs and output only
         got = torch.zeros(B, H * D, dtype=torch.bfloat16, device="cuda")
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        # the device's free memory, as the driver counts it, whoever allocates (the first call of a
+        # process may still load the kernel's code, so the comparison starts with the second)
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.ab_attention_decode_bf16_noalloc(_p(qkv), qkv.shape[1], _p(got), _p(k), _p(v), _p(table), W,
-                                                  _p(seq), _p(lens), B, H, K, D, ctypes.c_float(D ** -0.5), 0, ppc,
-                                                  n_chunks, stream)
+                                                  _p(seq), _p(lens), B, H, K, D, ctypes.c_float(D ** -0.5), window,
+                                                  ppc, n_chunks, stream)
         assert rc == 0, lib.ab_attention_decode_bf16_noalloc_error()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        if call:
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+        assert (got.double() - plain).abs().max().item() <= 1.6e-2
+        if empty_row is not None:
+            assert got[empty_row].float().abs().max().item() == 0.0, "a row without a sequence was written"
         # the same kernel with the same inputs: the tolerance of the kernel tests (bfloat16 outputs of order 1)
         err = (got.float() - want.float()).abs().max().item()
         assert err <= 1.6e-2, f"call {call}: max difference {err}"
@@ -92,3 +130,11 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
                                               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 2
     assert b"too large" in lib.ab_attention_decode_bf16_noalloc_error()
+    # the other limit alone: 8,193 tokens x 8 KV heads = 65,544 counters > 2^16, while the partial
+    # outputs (8,193 x 8 heads x 1 chunk x 8) stay below theirs
+    rc = lib.ab_attention_decode_bf16_noalloc(_p(dummy), 0, _p(dummy), _p(dummy), _p(dummy), _p(dummy), 1,
+                                              _p(dummy), _p(dummy), 8193, 8, 8, 8, ctypes.c_float(1.0), 0, 1, 1,
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 2
+    msg = lib.ab_attention_decode_bf16_noalloc_error()
+    assert b"65544 (limit 65536)" in msg and b"524352 (limit 1048576)" in msg
