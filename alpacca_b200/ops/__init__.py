@@ -395,7 +395,110 @@ def _decode_attention_plan(pairs: int, width: int, D: int, sms: int):
     return plan
 
 
+_STREAM_SCRATCH: dict = {}
+
+
+def _stream_scratch(device, n_partial: int, n_counters: int):
+    """Scratch of the streamed decode attention's merge through memory: partial outputs, their (maximum,
+    sum) pairs and zeroed arrival counters (every launch leaves them zero).  One set per device, used by
+    one launch after another in a stream; it only grows outside a graph capture."""
+    have = _STREAM_SCRATCH.get(device)
+    if have is None or have[0].numel() < n_partial or have[2].numel() < n_counters:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError(f"attention: scratch for {n_partial} partial sums needed during graph capture, "
+                              f"{0 if have is None else have[0].numel()} allocated before it")
+        n_partial = max(n_partial, 1 << 22)
+        have = (torch.empty(n_partial, dtype=torch.float32, device=device),
+                torch.empty(max(n_partial // 8, 1 << 16), dtype=torch.float32, device=device),
+                torch.zeros(max(n_counters, 1 << 16), dtype=torch.int32, device=device))
+        _STREAM_SCRATCH[device] = have
+    return have
+
+
+def attention_stream(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, fuse=0, pages_per_cta=8,
+                     merge="memory", ring=1):
+    """Decode attention that streams the cache through a ring of pages filled by TMA
+    (csrc/attention_stream.cu): head sizes 64 and 128, bfloat16.  A CTA takes `pages_per_cta` pages of
+    one (sequence, KV head); the chunks of a sequence are merged in chunk order, through scratch memory
+    (`merge` "memory") or inside a cluster of up to 8 ("cluster").  `ring`: 0 a short ring (four CTAs per
+    processor), 1 the usual one (two), 2 a deep one (one).  `fuse` as for the other decode kernel: 1 rotates q, 2 also rotates k
+    and appends k, v to the cache."""
+    lib = _lib("attention_stream")
+    k_pages, v_pages, table = cache.k, cache.v, cache.block_table
+    _cuda(qkv, out, k_pages, v_pages, table)
+    T = ctx.n_tokens
+    _need(lib.ab_attention_stream_supports(H, K, D) == 1, f"attention_stream: head size {D} is not 64 or 128")
+    _need(qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
+          and qkv.is_contiguous() and out.is_contiguous() and qkv.dim() == 2 and out.numel() >= T * H * D
+          and qkv.shape[-1] >= (H + (2 * K if fuse == 2 else 0)) * D and qkv.shape[0] >= T,
+          "attention_stream takes contiguous bfloat16 qkv [T,(H+2K)D], out [T,H*D]")
+    _need(tuple(k_pages.shape[1:]) == (K, 64, D) and k_pages.shape == v_pages.shape and k_pages.is_contiguous()
+          and v_pages.is_contiguous(), "attention_stream: cache pages [n_pages,K,64,D]")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous() and table.shape[0] >= T,
+          "block_table must be contiguous int32 [B,W]")
+    cos, sin, n_rot, pairing = rot if (rot is not None and fuse) else (None, None, 0, 0)
+    if cos is not None:
+        _cuda(cos, sin)
+        _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+              and sin.is_contiguous() and cos.shape == sin.shape and cos.shape[-1] == n_rot // 2 and n_rot % 16 == 0
+              and n_rot <= D, "rope tables must be float32 [P, n_rot/2], n_rot a multiple of 16")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _i32(ctx.kv_len, T, "kv_len")
+    width = max(int(table.shape[1]), 1)
+    ppc = max(1, min(int(pages_per_cta), width))
+    n_chunks = -(-width // ppc)
+    kind = 0
+    part_o = part_ml = arrivals = None
+    if n_chunks > 1:
+        if merge == "cluster" and n_chunks <= DECODE_MAX_CLUSTER:
+            kind = 1
+        else:
+            kind = 2
+            part_o, part_ml, arrivals = _stream_scratch(qkv.device, T * H * n_chunks * D, T * K * -(-(H // K) // 8))
+    _tc_unchecked["attention_stream"] = True
+    _check(lib.ab_attention_stream_bf16(
+        _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(arrivals), _p(k_pages), _p(v_pages),
+        k_pages.shape[0], _p(table), table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D,
+        ctypes.c_float(scale), int(window or 0), ppc, n_chunks, kind, int(ring), _p(cos), _p(sin), n_rot,
+        pairing, fuse, _stream()), "attention_stream")
+    return out
+
+
+STREAM_DECODE = True             # decode steps that read much cache: the streamed kernel (head sizes 64, 128)
+STREAM_MIN_BYTES = 40e6          # ... from this many bytes of cache per layer (by the block table's width)
+
+
+def _stream_plan(rows: int, H: int, K: int, D: int, width: int, sms: int):
+    """Whether the streamed decode attention should take a step of `rows` sequences whose block table is
+    `width` pages wide, and how: None, or (pages per CTA, merge, ring).  Measured on a B200 against the
+    other decode kernel at its best plan (microseconds per layer): 64 sequences of 530 tokens, 8 KV heads
+    of 64: 15.4 against 17.5; of 2,000 tokens: 48.4 against 55.3; 64 sequences of 128 to 2,048 tokens, 8
+    KV heads of 128: 63.1 against 100.9; 8 sequences of 16 to 1,024 tokens, 32 KV heads of 128: 17.9
+    against 31.6; 8 sequences of 3,800 tokens, 8 heads of 64: 15.5 against 18.4.  It loses where little
+    is read (8 sequences of 640 tokens: 6.9 against 5.1; one sequence: 5.4 against 4.75), hence the
+    threshold.  One CTA per (sequence, KV head) is best once there are more of those than processors;
+    fewer are cut into chunks that a cluster merges; many CTAs of few pages take the short ring."""
+    if not STREAM_DECODE or D not in (64, 128):
+        return None
+    pairs = rows * K * -(-(H // K) // 8)
+    if pairs * width * 64 * D * 4 < STREAM_MIN_BYTES:
+        return None
+    chunks = max(1, min(DECODE_MAX_CLUSTER, -(-3 * sms // (2 * pairs)), width))
+    ppc = -(-width // chunks)
+    ring = 0 if (pairs * chunks > 2 * sms and ppc <= 16) else 1
+    return ppc, "cluster", ring
+
+
 def _attention_decode(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fuse=0):
+    """Decode attention of one token per row of the batch: the kernel that fits the step's size."""
+    plan = _stream_plan(ctx.n_tokens, H, K, D, max(int(cache.block_table.shape[1]), 1), _sm_count(qkv.device))
+    if plan is not None:
+        return attention_stream(qkv, out, cache, ctx, H, K, D, scale, window, rot, fuse, pages_per_cta=plan[0],
+                                merge=plan[1], ring=plan[2])
+    return _attention_decode_mma(qkv, out, cache, ctx, H, K, D, scale, window, rot, fuse)
+
+
+def _attention_decode_mma(qkv, out, cache, ctx, H, K, D, scale, window, rot=None, fuse=0):
     """Decode attention: a CTA per (sequence, KV head, chunk of pages).  With few (sequence, head)
     pairs a CTA is large and a long table is cut into 2 to 8 chunks that are merged inside a
     thread-block cluster; with more pairs than processors the CTAs are smaller (several per
@@ -644,19 +747,22 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
     return out
 
 
-_tc_unchecked = {"gemm_tc": False, "attention_tc": False}   # tcgen05 kernels launched since the last check
+# kernels that wait on barriers with a limit, launched since the last check
+_tc_unchecked = {"gemm_tc": False, "attention_tc": False, "attention_stream": False}
 
 
 def check_tc_status() -> None:
-    """Raises `KernelError` if a tcgen05 kernel launched since the last call gave up waiting on a
-    barrier (its output is then unfinished).  Call it where the stream has just been synchronised:
-    it reads one word per library from the device, and nothing when no such kernel ran."""
-    for name, read in (("gemm_tc", gemm_tc_status), ("attention_tc", attention_tc_status)):
+    """Raises `KernelError` if a kernel that waits on barriers with a limit (the tcgen05 kernels, the
+    streamed decode attention), launched since the last call, gave up a wait (its output is then
+    unfinished).  Call it where the stream has just been synchronised: it reads one word per library
+    from the device, and nothing when no such kernel ran."""
+    for name, read in (("gemm_tc", gemm_tc_status), ("attention_tc", attention_tc_status),
+                       ("attention_stream", attention_stream_status)):
         if _tc_unchecked[name]:
             _tc_unchecked[name] = False
             code = read()
             if code:
-                raise KernelError(f"a tcgen05 kernel of {name} gave up waiting on a barrier (code {code}); "
+                raise KernelError(f"a kernel of {name} gave up waiting on a barrier (code {code}); "
                                   "the results of the steps since the last check are not valid")
 
 
@@ -668,3 +774,8 @@ def gemm_tc_status() -> int:
 def attention_tc_status() -> int:
     """0, or the code left by a tcgen05 attention kernel that gave up waiting on a barrier (synchronises)."""
     return _lib("attention_tc").ab_attention_tc_status()
+
+
+def attention_stream_status() -> int:
+    """0, or the code left by a streamed decode attention kernel that gave up waiting on a barrier (synchronises)."""
+    return _lib("attention_stream").ab_attention_stream_status()

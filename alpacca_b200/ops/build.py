@@ -139,7 +139,7 @@ def load(name: str) -> ctypes.CDLL:
         return lib
 
 
-ALL_LIBRARIES = ("elementwise", "attention_simt", "attention_mma", "gemm_f32", "gemv_bf16", "gemm_tc", "attention_tc", "sampling", "safetensors_reader")
+ALL_LIBRARIES = ("elementwise", "attention_simt", "attention_mma", "gemm_f32", "gemv_bf16", "gemm_tc", "attention_tc", "attention_stream", "sampling", "safetensors_reader")
 
 
 def build_all(names=ALL_LIBRARIES) -> list[Path]:

@@ -35,12 +35,24 @@ def load(model_dir, dtype, n, tokens_each=192):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n", ROWS)
-@pytest.mark.parametrize("name", ["B", "D", "E"])
-def test_logits_of_every_decode_step(model_dirs, name, n, dtype):
+@pytest.mark.parametrize("name", ["B", "D", "E", "D-streamed", "E-streamed"])
+def test_logits_of_every_decode_step(model_dirs, name, n, dtype, monkeypatch):
     """The prompts in one step, then four single-token steps through `Engine.step` and four replayed
     from the graph (which feeds on its own sampled tokens): the logits of every step against the
-    plain implementation's for the sequence as it stands."""
+    plain implementation's for the sequence as it stands.  "streamed": the decode attention that
+    streams the cache, which otherwise only takes steps that read tens of megabytes, takes every step."""
+    from alpacca_b200 import ops
     from alpacca_b200.engine.decode import bucket_rows
+    if name.endswith("-streamed"):
+        if dtype != "bfloat16":
+            pytest.skip("the streamed kernel is a bfloat16 kernel")
+        name = name[0]
+        monkeypatch.setattr(ops, "STREAM_MIN_BYTES", 0)
+        launched = []
+        real = ops.attention_stream
+        monkeypatch.setattr(ops, "attention_stream", lambda *a, **k: (launched.append(1), real(*a, **k))[1])
+    else:
+        launched = None
     from alpacca_b200.engine.step import StepEntry
     from alpacca_b200.sampling import DeviceSampler, SamplerParams
     d = model_dirs[(name, dtype)]
@@ -82,6 +94,8 @@ def test_logits_of_every_decode_step(model_dirs, name, n, dtype):
     for s in slots:
         eng.free_slot(s)
     eng.cache.check()
+    eng.wait()
+    assert launched is None or len(launched) >= 4 * len(model.decoder.spec.layers), "the streamed kernel did not run"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
