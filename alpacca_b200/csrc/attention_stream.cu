@@ -163,8 +163,8 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ arrivals,
                         bf16* __restrict__ k_out, bf16* __restrict__ v_out, const int* __restrict__ block_table,
-                        int table_width, const int* __restrict__ tok_seq, const int* __restrict__ kv_len, int H,
-                        int K, float scale_log2, int window, int pages_per_cta, int n_chunks, int merge,
+                        int table_width, const int* __restrict__ tok_seq, const int* __restrict__ kv_len,
+                        const int* __restrict__ row_order, int H, int K, float scale_log2, int window, int pages_per_cta, int n_chunks, int merge,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_rot, int pairing,
                         int fuse, int* __restrict__ status) {
   using Sm = StreamSmem<HD, STAGES>;
@@ -181,11 +181,13 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
   const int row_tiles = (G + 7) / 8;
-  const int tok = blockIdx.x;
+  // CTAs start in the order of their index: with `row_order` (the rows of the batch, longest sequence
+  // first) the long sequences start first and the short ones fill in behind them
+  const int tok = row_order ? row_order[blockIdx.x] : (int)blockIdx.x;
   const int kh = blockIdx.y / row_tiles, rt = blockIdx.y - kh * row_tiles;
   const int chunk = blockIdx.z;
-  // What is read before the wait was written in earlier steps (lengths, block table, every cached
-  // row but the one of this step's token), never by the kernels just before this one.
+  // What is read before the wait was written in earlier steps (lengths, block table, row order, every
+  // cached row but the one of this step's token), never by the kernels just before this one.
   const int* bt = block_table + (size_t)tok * table_width;
   const int b = tok_seq[tok];
   const int len = kv_len[tok];
@@ -492,14 +494,15 @@ AB_API int ab_attention_stream_stages(int D, int ring) {
 // Decode attention of one new token per row of the batch (see the head of this file).
 // qkv [n_tokens, q_stride] (q heads first, then k, v heads when fuse = 2), out [n_tokens, H*D], cache
 // pages [n_pages, K, 64, D]; block_table [n_tokens, table_width]; tok_seq[row] < 0: a row without a
-// sequence; kv_len[row]: the sequence's length with this step's token.
+// sequence; kv_len[row]: the sequence's length with this step's token; row_order (or null): a
+// permutation of the rows, the order in which their CTAs start (longest sequences first pays).
 // n_chunks chunks of pages_per_cta pages cover the table; `ring`: see ab_attention_stream_stages.  merge_kind: 1 = cluster (2..8 chunks), 2 =
 // scratch: part_o float [n_tokens*H*n_chunks, D], part_ml float [n_tokens*H*n_chunks, 2], arrivals int
 // [n_tokens * K * ceil(G/8)], zero before the first launch and left zero by every launch.
 AB_API int ab_attention_stream_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
                                     int* arrivals, void* k_pages, void* v_pages, int n_pages,
                                     const int* block_table, int table_width, const int* tok_seq, const int* kv_len,
-                                    int n_tokens, int H, int K, int D, float scale, int window, int pages_per_cta,
+                                    const int* row_order, int n_tokens, int H, int K, int D, float scale, int window, int pages_per_cta,
                                     int n_chunks, int merge_kind, int ring, const float* cos_t, const float* sin_t,
                                     int n_rot, int pairing, int fuse, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
@@ -563,7 +566,7 @@ AB_API int ab_attention_stream_bf16(const void* qkv, int q_stride, void* out, fl
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
     e = cudaLaunchKernelEx(&cfg, attention_stream_kernel<HDV, ST>, mk, mv, (const bf16*)qkv, q_stride, (bf16*)out,  \
                            part_o, part_ml, arrivals, (bf16*)k_pages, (bf16*)v_pages, block_table, table_width,     \
-                           tok_seq, kv_len, H, K, sl, window, pages_per_cta, n_chunks, merge, cos_t, sin_t, n_rot,  \
+                           tok_seq, kv_len, row_order, H, K, sl, window, pages_per_cta, n_chunks, merge, cos_t, sin_t, n_rot,  \
                            pairing, fuse, status);                                                                  \
   }
   if (D == 64) { if (ring <= 0) AS_GO(64, 3) else if (ring == 1) AS_GO(64, 6) else AS_GO(64, 12) }

@@ -77,8 +77,8 @@ class _Shape:
         R = dec.window
         n_groups = len(eng.cache.kv_groups)
         names = ["tokens", "tok_seq", "tok_pos", "cu_q", "kv_len", "slots", "want_rows", "rng_stream", "rng_step",
-                 "recent_pos", "seed"]
-        sizes = [rows, rows, rows, rows + 1, rows, rows, rows, rows, rows, rows, 2]
+                 "recent_pos", "seed", "row_order"]
+        sizes = [rows, rows, rows, rows + 1, rows, rows, rows, rows, rows, rows, 2, rows]
         sizes += [rows * width] * n_groups + [rows * R]
         self.offs = [0]
         for s in sizes:
@@ -117,7 +117,8 @@ class _Shape:
             n_tokens=self.rows, n_seqs=self.rows, n_want=self.rows, is_decode=True, max_q_len=1,
             max_kv_len=min(self.width * PAGE_SIZE, self.max_positions), tokens=self.d("tokens"), tok_seq=self.d("tok_seq"),
             tok_pos=self.d("tok_pos"), cu_q=self.d("cu_q"), kv_len=self.d("kv_len"), slots=self.d("slots"),
-            want_rows=self.d("want_rows"), block_tables=self.tables_dev(), wants_every_row=True)
+            want_rows=self.d("want_rows"), block_tables=self.tables_dev(), wants_every_row=True,
+            row_order=self.d("row_order"))
 
 
 class GraphDecoder:
@@ -162,6 +163,7 @@ class GraphDecoder:
         sh.d("tok_seq").fill_(-1)
         sh.d("cu_q").copy_(torch.arange(sh.rows + 1, dtype=torch.int32))
         sh.d("want_rows").copy_(torch.arange(sh.rows, dtype=torch.int32))
+        sh.d("row_order").copy_(torch.arange(sh.rows, dtype=torch.int32))
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -211,6 +213,10 @@ class GraphDecoder:
         sh.h("kv_len").zero_()
         sh.h("kv_len")[:n] = torch.tensor(lens, dtype=torch.int32) + 1
         sh.h("slots").copy_(torch.tensor(slots, dtype=torch.int32))
+        # the rows, longest sequence first (the sequences grow in step, so the order holds for the
+        # layout's life); rows without a sequence come last
+        sh.h("row_order").copy_(torch.tensor(sorted(range(sh.rows), key=lambda r: -lens[r] if r < n else 1),
+                                             dtype=torch.int32))
         sh.h("want_rows").copy_(torch.arange(sh.rows, dtype=torch.int32))
         sh.h("rng_stream").zero_()
         sh.h("rng_stream")[:n] = torch.tensor([st.stream for _, _, st in live], dtype=torch.int32)

@@ -40,6 +40,8 @@ class StepContext:
     host_q_lens: list = None
     host_kv_lens: list = None
     wants_every_row: bool = False    # want_rows is 0, 1, .., n_tokens - 1: each row's logits, in order
+    row_order: torch.Tensor = None   # int32 [n_seqs], decode steps: the batch rows, longest sequence first
+                                     # (kernels that give a row to a CTA start the long rows first)
     extras: dict = field(default_factory=dict)   # per-step plans of kernels (tile lists and the like)
 
 
@@ -78,7 +80,8 @@ class ContextBuilder:
         T = sum(q_lens)
         n_want = sum(len(e.want) for e in entries)
         widths = [cache.table_width(g, [e.slot for e in entries]) for g in range(len(cache.kv_groups))]
-        sizes = [T, T, T, B + 1, B, B, n_want] + [B * w for w in widths]
+        decode = all(q == 1 for q in q_lens)
+        sizes = [T, T, T, B + 1, B, B, n_want] + [B * w for w in widths] + [B if decode else 0]
         offs = [0]
         for s in sizes:
             offs.append(offs[-1] + _pad4(max(s, 1)))
@@ -102,6 +105,9 @@ class ContextBuilder:
         for g, w in enumerate(widths):
             view = stage[offs[7 + g]:offs[7 + g] + B * w].view(B, w)
             cache.fill_block_table(g, [e.slot for e in entries], view, w)
+        i_order = 7 + len(widths)
+        if decode:
+            host[offs[i_order]:offs[i_order] + B] = np.argsort(-kv, kind="stable")
         dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(stage[:total], non_blocking=True)
         if self.pinned:
@@ -112,7 +118,7 @@ class ContextBuilder:
         def part(i, n):
             return dev[offs[i]:offs[i] + n]
         return StepContext(
-            n_tokens=T, n_seqs=B, n_want=n_want, is_decode=all(q == 1 for q in q_lens),
+            n_tokens=T, n_seqs=B, n_want=n_want, is_decode=decode, row_order=part(i_order, B) if decode else None,
             max_q_len=max(q_lens), max_kv_len=int(kv.max()),
             tokens=part(0, T), tok_seq=part(1, T), tok_pos=part(2, T), cu_q=part(3, B + 1),
             kv_len=part(4, B), slots=part(5, B), want_rows=part(6, n_want),

@@ -444,6 +444,10 @@ def attention_stream(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, f
               and n_rot <= D, "rope tables must be float32 [P, n_rot/2], n_rot a multiple of 16")
     _i32(ctx.tok_seq, T, "tok_seq")
     _i32(ctx.kv_len, T, "kv_len")
+    order = getattr(ctx, "row_order", None)      # a permutation of the rows, longest sequence first
+    if order is not None:
+        _cuda(order)
+        _i32(order, T, "row_order")
     width = max(int(table.shape[1]), 1)
     ppc = max(1, min(int(pages_per_cta), width))
     n_chunks = -(-width // ppc)
@@ -458,7 +462,7 @@ def attention_stream(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, f
     _tc_unchecked["attention_stream"] = True
     _check(lib.ab_attention_stream_bf16(
         _p(qkv), qkv.shape[-1], _p(out), _p(part_o), _p(part_ml), _p(arrivals), _p(k_pages), _p(v_pages),
-        k_pages.shape[0], _p(table), table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), T, H, K, D,
+        k_pages.shape[0], _p(table), table.shape[1], _p(ctx.tok_seq), _p(ctx.kv_len), _p(order), T, H, K, D,
         ctypes.c_float(scale), int(window or 0), ppc, n_chunks, kind, int(ring), _p(cos), _p(sin), n_rot,
         pairing, fuse, _stream()), "attention_stream")
     return out
