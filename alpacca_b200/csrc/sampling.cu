@@ -230,9 +230,11 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   }
 
   // ---- weight above t_k (or of everything) ---------------------------------
+  // (only the cuts need it: plain temperature sampling goes straight to the walk)
+  const bool use_p = top_p > 0.f && top_p < 1.f;
   unsigned long long w_gt = 0;
   unsigned long long w_tk = 0;   // weight of one element equal to t_k
-  for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+  if (use_k || use_p) for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
     const float v = l[i];
     const unsigned int key = float_key(v);
     if (!use_k || key > tk_key) w_gt += weight_fx(v, m, inv_t);
@@ -258,7 +260,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   unsigned int t_key = use_k ? tk_key : 0u;
   unsigned int c_ties = use_k ? ck : 0u;        // ties at t_key that are kept
   bool ties_limited = use_k;                    // false: every element with key >= t_key is kept
-  if (top_p > 0.f && top_p < 1.f) {
+  if (use_p) {
     const unsigned long long P = (unsigned long long)((double)w_k * (double)top_p);
     if (use_k && P > w_gt) {
       // the cut falls among the ties at t_k
@@ -320,31 +322,53 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   }
 
   // ---- walk the kept set in index order ---------------------------------------
-  const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-  const int i0 = tid * chunk, i1 = min(vocab, i0 + chunk);
-  unsigned int my_ties = 0;
-  if (ties_limited)
-    for (int i = i0; i < i1; ++i) my_ties += float_key(l[i]) == t_key;
-  unsigned long long we, wt;
-  unsigned int tie_rank, ties_total;
-  block_scan(0ull, my_ties, &we, &tie_rank, &wt, &ties_total, &sh);
+  // Warp w owns the indices [w * seg, (w + 1) * seg); its lanes read them 32 at a time, side by side
+  // (whole lines of memory per load), so "index order" inside a warp is (round, lane).  A tie's rank
+  // in index order is the number of ties before it: the warps before (a scan of 32 counts), the
+  // rounds before and the lanes before (a ballot).  The kept weight of the warps is scanned the same
+  // way; the warp whose share holds the target walks its segment once more to find the index.
+  const int seg = (vocab + 31) / 32;
+  const int s0 = min(vocab, warp * seg), s1 = min(vocab, s0 + seg);
+  const unsigned int lanes_before = (1u << lane) - 1u;
+  unsigned int ties_before = 0;             // ties in the warps before this one
+  if (ties_limited) {
+    unsigned int n = 0;
+    for (int i = s0 + lane; i < s1; i += 32) n += float_key(l[i]) == t_key;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    unsigned long long we, wt;
+    unsigned int ct;
+    block_scan(0ull, lane == 0 ? n : 0u, &we, &ties_before, &wt, &ct, &sh);
+    ties_before = __shfl_sync(0xffffffffu, ties_before, 0);
+  }
+  // kept weight of lane's elements of one round; `rank` = ties seen so far in index order
+  auto kept_weight = [&](int i, unsigned int& rank) -> unsigned long long {
+    const bool in = i < s1;
+    const float v = in ? l[i] : 0.f;
+    const unsigned int key = float_key(v);
+    bool keep = in;
+    if (ties_limited) {
+      const unsigned int tie = __ballot_sync(0xffffffffu, in && key == t_key);
+      if (key > t_key) keep = in;
+      else if (key == t_key) keep = in && (rank + __popc(tie & lanes_before)) < c_ties;
+      else keep = false;
+      rank += __popc(tie);
+    }
+    return keep ? weight_fx(v, m, inv_t) : 0ull;
+  };
   unsigned long long my_w = 0;
   {
-    unsigned int rank = tie_rank;
-    for (int i = i0; i < i1; ++i) {
-      const float v = l[i];
-      const unsigned int key = float_key(v);
-      bool keep;
-      if (!ties_limited) keep = true;
-      else if (key > t_key) keep = true;
-      else if (key == t_key) keep = rank++ < c_ties;
-      else keep = false;
-      if (keep) my_w += weight_fx(v, m, inv_t);
-    }
+    unsigned int rank = ties_before;
+    for (int i0 = s0; i0 < s1; i0 += 32) my_w += kept_weight(i0 + lane, rank);
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) my_w += __shfl_xor_sync(0xffffffffu, my_w, o);     // the warp's kept weight
   unsigned long long w_before, w_total;
-  unsigned int ce, ct;
-  block_scan(my_w, 0u, &w_before, &ce, &w_total, &ct, &sh);
+  {
+    unsigned int ce, ct;
+    block_scan(lane == 0 ? my_w : 0ull, 0u, &w_before, &ce, &w_total, &ct, &sh);
+    w_before = __shfl_sync(0xffffffffu, w_before, 0);
+  }
 
   if (seed_dev) {            // the seed lives on the device when the launch is replayed from a graph
     seed_lo = seed_dev[0];
@@ -357,19 +381,23 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   if (tid == 0) sh.result = sh.arg;     // fallback: the maximum (always kept)
   __syncthreads();
   if (my_w > 0 && w_before <= target && target < w_before + my_w) {
+    // this warp's share holds the target: the first index at which the running weight exceeds it
     unsigned long long acc = w_before;
-    unsigned int rank = tie_rank;
-    for (int i = i0; i < i1; ++i) {
-      const float v = l[i];
-      const unsigned int key = float_key(v);
-      bool keep;
-      if (!ties_limited) keep = true;
-      else if (key > t_key) keep = true;
-      else if (key == t_key) keep = rank++ < c_ties;
-      else keep = false;
-      if (!keep) continue;
-      acc += weight_fx(v, m, inv_t);
-      if (acc > target) { sh.result = i; break; }
+    unsigned int rank = ties_before;
+    for (int i0 = s0; i0 < s1; i0 += 32) {
+      const unsigned long long w = kept_weight(i0 + lane, rank);
+      unsigned long long incl = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const unsigned int hit = __ballot_sync(0xffffffffu, w > 0 && acc + incl > target);
+      if (hit) {
+        if (lane == __ffs(hit) - 1) sh.result = i0 + lane;
+        break;
+      }
+      acc += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
   __syncthreads();
