@@ -212,7 +212,8 @@ def measure_decode(model, shape, batch, steps, warmup, seed=0):
         eager_launches = ops.launches - before
         per_step = getattr(decoder, "kernels_per_step", None) or (eager_launches // max(steps, 1))
         # step i reads the held0 + i * batch tokens cached so far (and appends one per sequence)
-        return batch * steps / (ms / 1e3), ms / steps, held0 + batch * (steps - 1) / 2.0, per_step
+        measure_decode.last_held = held0 + batch * (steps - 1) / 2.0
+        return batch * steps / (ms / 1e3), ms / steps, measure_decode.last_held, per_step
     finally:
         for s in slots:
             model.engine.free_slot(s)
@@ -278,31 +279,41 @@ def run_ours(args):
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(0)
     pk = peaks()
-    shape = SHAPES[args.shape]
+    shape = dict(SHAPES[args.shape])
+    if args.only == "decode" and args.prompt_len:
+        shape["prompt_lengths"] = (args.prompt_len, args.prompt_len)
+    if args.only == "prefill" and args.prefill_tokens:
+        shape["prefill_tokens"] = args.prefill_tokens
+        shape["context"] = max(shape["context"], args.prefill_tokens)
     cfg = dict(shape["config"])
     layers_full = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     batch = args.batch or shape["batch"]
     steps = args.steps or shape["steps"]
-    biggest = max([batch, *shape["points"]])
+    biggest = max([batch, *shape["points"]]) if args.only == "all" else batch
     model = Model.random(cfg, seed=0, n_ctx=shape["context"], dtype="bfloat16", max_batch=biggest)
     weights = model_bytes(model)
     kv_per_token = sum(g.bytes_per_token for g in model.engine.cache.kv_groups)
 
     if args.only == "decode":
         tps, ms_step, _, kernels = measure_decode(model, shape, batch, steps, args.warmup)
+        held = measure_decode.last_held
+        gbs = (weights + held * kv_per_token) / (ms_step / 1e3) / 1e9
         print(json.dumps({"only": "decode", "shape": args.shape, "batch": batch, "tok_s": round(tps, 1),
-                          "ms_per_step": round(ms_step, 4), "kernels_per_step": kernels}))
+                          "ms_per_step": round(ms_step, 4), "kernels_per_step": kernels,
+                          "tokens_held": int(held), "gb_s": round(gbs, 1), "of_hbm_peak": round(gbs / pk["hbm_gbs"], 3)}))
         return 0
     if shape["prefill_tokens"]:
         pre_prompts = workload_prompts(dict(shape, prompt_lengths=(shape["prefill_tokens"],) * 2), 1, seed=2)
     else:
         pre_prompts = workload_prompts(shape, batch, seed=0)        # the prompts that the decode run starts from
     if args.only == "prefill":
-        pre_ms = measure_prefill(model, pre_prompts, runs=max(steps, 1))
+        pre_ms = measure_prefill(model, pre_prompts, runs=max(args.steps, 1))
+        fl = prefill_flops(cfg, [len(p) for p in pre_prompts])
         print(json.dumps({"only": "prefill", "shape": args.shape, "tokens": sum(map(len, pre_prompts)),
-                          "ms": round(pre_ms, 3)}))
+                          "ms": round(pre_ms, 3), "tok_s": round(sum(map(len, pre_prompts)) / (pre_ms / 1e3), 1),
+                          "of_bf16_peak": round(fl / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
         return 0
 
     clocks = ClockSampler()
@@ -492,6 +503,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs)")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="with --only decode: equal prompts of this many tokens instead of the workload's")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help="with --only prefill: one prompt of this many tokens instead of the workload's")
     args = ap.parse_args()
     n = int(os.environ.get("WORLD_SIZE", args.gpus))
     if args.gpus > 1 or n > 1:
