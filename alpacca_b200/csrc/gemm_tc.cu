@@ -368,6 +368,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #define TP_STAGE_BYTES (TP_A_BYTES + TP_B_BYTES)
 #define TP_SMEM (TP_STAGES * TP_STAGE_BYTES + 1024 + 256)
 
+// The order in which the tiles are walked: bands of TP_BAND tile rows; inside a band one tile column
+// after the other, the band's rows of a column side by side.  The CTAs that run at the same time
+// (consecutive tiles) then share a band of X (16 x 128 rows: it stays in the L2 for all columns) and a
+// few column tiles of W, so W is read once per band and X once: with rows fastest over the whole
+// matrix, as before, a prompt of 65,536 tokens re-read X for every tile column (60 GB at the 8B sizes,
+// as long as the arithmetic takes).
+#define TP_BAND 16
+__device__ __forceinline__ void tp_tile_origin(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+  const int per_band = TP_BAND * tiles_n;
+  const int band = tile / per_band, within = tile - band * per_band;
+  const int rows = min(TP_BAND, tiles_m - band * TP_BAND);
+  const int col = within / rows;
+  m0 = (band * TP_BAND + (within - col * rows)) * TC_BM;
+  n0 = col * TP_BN;
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -382,6 +398,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb = (K + TC_BK - 1) / TC_BK;
+  const int tiles_n = n_tiles / tiles_m;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TP_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
@@ -404,7 +421,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
       bool ok = true;
       const int first = blockIdx.x;
       const int early = first < n_tiles ? min(nkb, TP_STAGES) : 0;
-      const int n0_first = (first / tiles_m) * TP_BN, m0_first = (first % tiles_m) * TC_BM;
+      int n0_first = 0, m0_first = 0;
+      if (first < n_tiles) tp_tile_origin(first, tiles_m, tiles_n, m0_first, n0_first);
       for (int i = 0; i < early; ++i) {
         mbar_expect_tx(full + i, TP_STAGE_BYTES);
         tma_load_2d(base + i * TP_STAGE_BYTES + TP_A_BYTES, &map_w, i * TC_BK, n0_first, full + i);
@@ -413,7 +431,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
       pdl_trigger();
       for (int i = 0; i < early; ++i) tma_load_2d(base + i * TP_STAGE_BYTES, &map_x, i * TC_BK, m0_first, full + i);
       for (int tile = first; tile < n_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TP_BN;
+        int m0, n0;
+        tp_tile_origin(tile, tiles_m, tiles_n, m0, n0);
         for (int kb = (tile == first ? early : 0); kb < nkb; ++kb) {
           const int i = it + kb;
           const int s = i % TP_STAGES;
@@ -460,7 +479,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
       const int buf = lt & 1;
-      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TP_BN;
+      int m0, n0;
+      tp_tile_origin(tile, tiles_m, tiles_n, m0, n0);
       ok = mbar_wait(acc_full + buf, (lt >> 1) & 1);
       if (!ok) atomicExch(status, 14);
       ok = __all_sync(0xffffffffu, ok);      // tcgen05.ld below is warp-wide
