@@ -2,6 +2,7 @@
 
     python -m alpacca_b200 run MODEL [PROMPT ...] [--ctx N] [--temp T] [--top-k K] [--top-p P]
                                [--repeat-penalty R] [--seed S] [--n-predict N]
+    python -m alpacca_b200 show MODEL [--tensors]
 
 The flags are the reference's (`_add_model_flags`, alpacca/cli.py:662-671)
 with its defaults (alpacca/sample.py:12-19).  MODEL is a model folder; a
@@ -79,6 +80,40 @@ def cmd_run(args) -> int:
     return 0
 
 
+def cmd_show(args) -> int:
+    """What a model folder holds, as the reference's `show` (alpacca/cli.py:240-259) does for an
+    installed model: the configuration, the files and, with --tensors, the tensor table (the
+    reference's --metadata).  It reads the folder only: no GPU is needed."""
+    import json
+    from pathlib import Path
+    from .config import load_config
+    from .engine.loading import build_model
+    from .weights import FolderSource, check_names
+    folder = Path(args.model)
+    config = load_config(folder)
+    print(json.dumps(config.to_dict(), indent=2))
+    print(f"\nfiles in {folder}:")
+    for f in sorted(folder.iterdir()):
+        if f.is_file():
+            print(f"  {f.name:<36} {f.stat().st_size / 2**20:10.1f} MiB")
+    source = FolderSource(folder)
+    try:
+        table = source.table()
+        model = build_model(config, device="cpu")
+        check_names(model.param_specs(), table, where=str(folder))     # one error with everything that does not fit
+        n = sum(int(__import__("math").prod(shape)) for _, shape in table.values())
+        print(f"\n{config.architecture}: {len(model.spec.layers)} layers, {len(table)} tensors, "
+              f"{n / 1e6:.1f}M parameters, positions up to {config.max_positions}; "
+              f"every tensor the model expects is there with its shape")
+        if args.tensors:
+            print("\ntensors:")
+            for name, (dtype, shape) in sorted(table.items()):
+                print(f"  {name:<56} {dtype:<5} {list(shape)}")
+    finally:
+        source.close()
+    return 0
+
+
 def cmd_make_random(args) -> int:
     import json
     from .engine.loading import write_random_model_dir
@@ -104,6 +139,11 @@ def main(argv=None) -> int:
     p.add_argument("prompt", nargs="*")
     add_run_flags(p)
     p.set_defaults(func=cmd_run)
+
+    p = sub.add_parser("show", help="show a model folder's configuration, files and tensors")
+    p.add_argument("model")
+    p.add_argument("--tensors", action="store_true", help="list every tensor with dtype and shape")
+    p.set_defaults(func=cmd_show)
 
     p = sub.add_parser("make-random", help="write a model folder with random weights from a config.json")
     p.add_argument("config", help="a config.json of a registered architecture")

@@ -41,3 +41,16 @@ def test_exit_codes(capsys):
     assert cli.main([]) == 0
     assert cli.main(["run", "/nonexistent/model", "1 2"]) == 1
     assert "alpacca_b200: error:" in capsys.readouterr().err
+
+
+def test_show_reads_a_folder_without_a_gpu(tmp_path, capsys):
+    import tiny
+    from alpacca_b200.engine.loading import write_random_model_dir
+    d = write_random_model_dir(tmp_path / "m", tiny.TINY_C, 3, dtype="bfloat16")
+    assert cli.main(["show", str(d), "--tensors"]) == 0
+    out = capsys.readouterr().out
+    assert '"hidden_size": 120' in out and "model.safetensors" in out and "4 layers" in out
+    assert "model.layers.3.self_attn.q_proj.bias" in out and "BF16" in out
+    (d / "config.json").write_text((d / "config.json").read_text().replace('"hidden_size": 120', '"hidden_size": 128'))
+    assert cli.main(["show", str(d)]) == 1
+    assert "shape" in capsys.readouterr().err

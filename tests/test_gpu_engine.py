@@ -3,6 +3,7 @@ whole requests, the last 32 tokens one by one, unequal batches one after another
 with slots used again, long decoding, the first tokens of a sequence."""
 import numpy as np
 import pytest
+import torch
 
 import tiny
 from helpers import CONFIGS, check_logits, plain_logits
@@ -206,3 +207,65 @@ def test_norms_inside_the_products_change_no_result(model_dirs, name, monkeypatc
     assert runs[True][1] < runs[False][1], "the norms still ran as kernels of their own"
     from helpers import logit_tolerances
     assert np.abs(runs[True][0] - runs[False][0]).max() <= logit_tolerances(runs[False][0], "bfloat16")[0]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_only_a_sequence_s_own_positions_are_written(model_dirs, name, dtype, monkeypatch):
+    """Canaries: the whole cache holds a huge value before the run.  After prompts of unequal lengths,
+    single-token steps and steps replayed from a graph whose shape has more rows than sequences, exactly
+    positions 0 .. length-1 of each sequence's own pages hold keys and values, in every layer and head,
+    and everything else still holds the canary: no kernel wrote beside its place (a padded row, a page of
+    another sequence, a position past the end), and none read one (the logits are the plain model's)."""
+    from alpacca_b200 import ops
+    from alpacca_b200.api import Model
+    from alpacca_b200.engine import StepEntry
+    from alpacca_b200.sampling import DeviceSampler, SamplerParams
+    CANARY = 1.0e30
+    d = model_dirs[(name, dtype)]
+    cfg = CONFIGS[name]
+    if dtype == "bfloat16":
+        monkeypatch.setattr(ops, "STREAM_MIN_BYTES", 0)        # the streamed decode attention where it can run
+    model = Model.load(d, dtype=dtype, max_batch=8, max_tokens=64 * 24)
+    eng = model.engine
+    for grp in eng.cache.kv_groups:
+        grp.k.fill_(CANARY)
+        grp.v.fill_(CANARY)
+    prompts = [tiny.prompt_tokens(cfg, n, 1100 + i) for i, n in enumerate((1, 63, 64, 65, 130))]
+    slots = [eng.alloc_slot() for _ in prompts]
+    sampler = DeviceSampler(SamplerParams.greedy(), eng.device)
+    states = [sampler.new_state(i, p) for i, p in enumerate(prompts)]
+    seqs = [list(p) for p in prompts]
+    logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+    toks = sampler.sample(logits, states)
+    for _ in range(2):                                  # step by step
+        for q, t in zip(seqs, toks):
+            q.append(t)
+        logits = eng.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks)])
+        toks = sampler.sample(logits, states)
+    dec = model.decoder_for(sampler)                    # five sequences in a shape of eight rows
+    live = [(s, t, st) for s, t, st in zip(slots, toks, states)]
+    for _ in range(3):
+        for q, (_, t, _) in zip(seqs, live):
+            q.append(t)
+        toks = dec.step(live)
+        live = [(s, t, st) for (s, _, st), t in zip(live, toks)]
+    last = dec.shape.logits[:len(seqs)].cpu().numpy()
+    eng.wait()
+    assert np.isfinite(last).all()
+    for b, q in enumerate(seqs):
+        check_logits(last[b], plain_logits(d, q)[-1], dtype, f"{name} canaries, sequence {b}")
+    for grp in eng.cache.kv_groups:
+        own = torch.zeros(grp.n_pages, 64, dtype=torch.bool)
+        for s in slots:
+            pages = grp.page_lists[s]
+            for pos in range(eng.length(s)):
+                own[pages[pos // 64], pos % 64] = True
+        for what, t in (("keys", grp.k), ("values", grp.v)):
+            written = (t != CANARY).cpu()               # [entry, page, head, position, dim]
+            everywhere = written.all(dim=4).all(dim=2).all(dim=0)
+            anywhere = written.any(dim=4).any(dim=2).any(dim=0)
+            assert torch.equal(anywhere, own), f"{what}: {int((anywhere & ~own).sum())} places written that no sequence owns"
+            assert torch.equal(everywhere, own), f"{what}: {int((own & ~everywhere).sum())} owned places not written in full"
+    for s in slots:
+        eng.free_slot(s)
