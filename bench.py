@@ -322,9 +322,12 @@ def run_ours(args):
     clock_info = clocks.stop()
 
     e2e_tps, _ = measure_e2e(model, shape, batch, steps)
+    # the points: at least 64 timed steps after at least 16 untimed ones, so that a short run's figure
+    # is not that of the few milliseconds after the prompt step (which runs into the power cap at batch 64)
     points = {}
     for b in shape["points"]:
-        points[f"decode_b{b}"] = round(measure_decode(model, shape, b, steps, args.warmup, seed=10 + b)[0], 1)
+        points[f"decode_b{b}"] = round(measure_decode(model, shape, b, max(steps, 64), max(args.warmup, 16),
+                                                      seed=10 + b)[0], 1)
     pre_ms = measure_prefill(model, pre_prompts)
     pre_tokens = sum(map(len, pre_prompts))
     flops = prefill_flops(cfg, [len(p) for p in pre_prompts])
