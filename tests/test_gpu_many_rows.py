@@ -35,12 +35,14 @@ def load(model_dir, dtype, n, tokens_each=192):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n", ROWS)
-@pytest.mark.parametrize("name", ["B", "D", "E", "D-streamed", "E-streamed"])
+@pytest.mark.parametrize("name", ["B", "C", "D", "E", "D-streamed", "E-streamed"])
 def test_logits_of_every_decode_step(model_dirs, name, n, dtype, monkeypatch):
     """The prompts in one step, then four single-token steps through `Engine.step` and four replayed
     from the graph (which feeds on its own sampled tokens): the logits of every step against the
     plain implementation's for the sequence as it stands.  "streamed": the decode attention that
-    streams the cache, which otherwise only takes steps that read tens of megabytes, takes every step."""
+    streams the cache, which otherwise only takes steps that read tens of megabytes, takes every step.
+    ("C" has five KV heads: 64 sequences are 320 (sequence, KV head) pairs, more than the device has
+    processors, so the other decode kernel takes its small CTAs, several per processor.)"""
     from alpacca_b200 import ops
     from alpacca_b200.engine.decode import bucket_rows
     if name.endswith("-streamed"):
