@@ -59,6 +59,33 @@ def test_greedy_generation_of_an_unequal_batch(model_dirs, name, dtype, graphs):
     assert model.engine.cache.slots.n_held == 0
 
 
+def test_graph_steps_beyond_the_context_are_refused(model_dirs):
+    """Replaying more steps than a sequence has positions left would write past its pages and read past
+    the rotation tables: the decoder refuses before it launches, and leaves the lengths as they were."""
+    from alpacca_b200.api import Model
+    from alpacca_b200.cache import CacheFull
+    from alpacca_b200.engine.step import StepEntry
+    from alpacca_b200.sampling import DeviceSampler, SamplerParams
+    d = model_dirs[("a", "bfloat16")]
+    model = Model.load(d, dtype="bfloat16", n_ctx=32, max_batch=2)
+    eng = model.engine
+    sampler = DeviceSampler(SamplerParams.greedy(), eng.device)
+    p = tiny.prompt_tokens(tiny.TINY_A, 20, 770)
+    slot = eng.alloc_slot()
+    st = sampler.new_state(0, p)
+    tok = sampler.sample(eng.step([StepEntry(slot, p, [19])]), [st])[0]
+    dec = model.decoder_for(sampler)
+    live = [(slot, tok, st)]
+    dec.run(live, 10)                       # positions 20 .. 29
+    assert eng.length(slot) == 30
+    with pytest.raises(CacheFull, match="context window full"):
+        dec.run(live, 3)                    # 30, 31 are left: three steps do not fit
+    assert eng.length(slot) == 30
+    dec.run(live, 2)
+    assert eng.length(slot) == 32
+    eng.free_slot(slot)
+
+
 def test_stop_token_and_context_end_sequences(model_dirs):
     from alpacca_b200.api import Model, generate
     from alpacca_b200.sampling import SamplerParams

@@ -33,3 +33,17 @@ def test_good_entries_come_back_as_int32_arrays():
 def test_faulty_entries_are_refused(entries, needle):
     with pytest.raises(ValueError, match=needle):
         check(entries)
+
+
+def test_an_engine_cannot_have_more_positions_than_its_model_was_built_for():
+    """Tables indexed by position (the rotation's angles) have as many rows as the model was built for;
+    an engine that let sequences grow beyond them would have the kernels read past their end."""
+    import torch
+    from alpacca_b200.parts.base import BuildOptions
+    model = SimpleNamespace(opts=BuildOptions(dtype=torch.float32, device="cpu", max_positions=128),
+                            cache_entry_specs=lambda: [], spec=SimpleNamespace(vocab_size=10))
+    eng = Engine(model, max_tokens=256, max_slots=2)
+    assert eng.max_positions == 128
+    assert Engine(model, max_tokens=256, max_slots=2, max_positions=64).max_positions == 64
+    with pytest.raises(ValueError, match="built\\s+for 128"):
+        Engine(model, max_tokens=256, max_slots=2, max_positions=129)
