@@ -57,11 +57,73 @@ def _cuda(*tensors):
 
 
 launches = 0     # kernels of this package launched so far (the benchmark reports the count)
+_timeline = None  # while `timers()` is active: [(operation, event recorded after its launch), ...]
+
+
+class Timers:
+    """Device time per kind of operation, for steps that are issued one launch after the other (not for
+    graph replays).  An event is recorded after every launch of this package (and after the library
+    products it calls); an operation's time is the time from the event before it to its own, so what
+    the device idles between two launches counts for the later one.
+
+        with ops.timers() as t:
+            engine.step(entries)
+        print(t.table())
+    """
+
+    def __init__(self):
+        self.marks = []
+
+    def __enter__(self):
+        global _timeline
+        if _timeline is not None:
+            raise KernelError("ops.timers() is already active")
+        torch.cuda.synchronize()
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        self.marks = [("start", start)]
+        _timeline = self.marks
+        return self
+
+    def __exit__(self, *exc):
+        global _timeline
+        _timeline = None
+        torch.cuda.synchronize()
+        return False
+
+    def totals(self) -> dict:
+        """{operation: (launches, microseconds)} in the order of first appearance."""
+        out: dict = {}
+        for (_, before), (what, after) in zip(self.marks, self.marks[1:]):
+            n, us = out.get(what, (0, 0.0))
+            out[what] = (n + 1, us + before.elapsed_time(after) * 1e3)
+        return out
+
+    def table(self) -> str:
+        tot = self.totals()
+        whole = sum(us for _, us in tot.values()) or 1.0
+        lines = [f"{'operation':<24} {'launches':>8} {'us':>10} {'share':>7}"]
+        for what, (n, us) in sorted(tot.items(), key=lambda kv: -kv[1][1]):
+            lines.append(f"{what:<24} {n:>8} {us:>10.1f} {100 * us / whole:>6.1f}%")
+        lines.append(f"{'total':<24} {sum(n for n, _ in tot.values()):>8} {whole:>10.1f}")
+        return "\n".join(lines)
+
+
+def timers() -> Timers:
+    return Timers()
+
+
+def _mark(what):
+    if _timeline is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        _timeline.append((what, ev))
 
 
 def _check(rc, what):
     global launches
     launches += 1
+    _mark(what)
     if rc != 0:
         if rc >= 1000:
             raise KernelError(f"{what}: CUDA error {rc - 1000} at launch")
@@ -637,6 +699,7 @@ def linear_bf16(x, w, out, n_rows=None, bias=None, start_early=True, owed=None):
         torch.mm(xs, w.t(), out_dtype=torch.float32, out=ys)
     else:
         torch.mm(xs, w.t(), out=ys)
+    _mark("library product")
     if bias is not None:
         add_bias(ys, bias)
     return out

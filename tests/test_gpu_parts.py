@@ -170,3 +170,24 @@ def test_block(dtype):
     y = y + plain.linear(plain.swiglu(plain.linear(hn, w["m.gate_proj.weight"]), plain.linear(hn, w["m.up_proj.weight"])),
                          w["m.down_proj.weight"])
     close(got, y, dtype)
+
+
+def test_timers_attribute_device_time_to_operations(model_dirs):
+    """`ops.timers()`: a prompt step issued launch by launch gives a time for every kind of operation
+    that ran, and nothing is recorded outside the `with`."""
+    import tiny
+    from alpacca_b200 import ops
+    from alpacca_b200.engine import Engine, StepEntry
+    from alpacca_b200.engine.loading import load_model_dir
+    eng = Engine(load_model_dir(model_dirs[("d", "bfloat16")], dtype="bfloat16"), max_tokens=64 * 8, max_slots=2)
+    toks = tiny.prompt_tokens(tiny.TINY_D, 200, 5)
+    slot = eng.alloc_slot()
+    with ops.timers() as t:
+        eng.step([StepEntry(slot, toks, [199])])
+    tot = t.totals()
+    assert {"embed_rows", "add_rmsnorm", "rope_append", "library product"} <= set(tot), tot
+    assert any(k.startswith("attention") for k in tot) and all(us > 0 for _, us in tot.values())
+    assert tot["add_rmsnorm"][0] == 2 * 2 + 1 and "total" in t.table()
+    n = len(t.marks)
+    eng.step([StepEntry(slot, [toks[0]], [0])])
+    assert len(t.marks) == n and ops._timeline is None
