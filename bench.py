@@ -20,7 +20,10 @@ point (`alpacca_b200.api.generate`): token ids in from host lists, token ids out
 the per-step host traffic that serving has.  `prefill` is the 2,048-token prompt (1b) or the
 workload's own unequal batch of prompts in one step (7b, 8b); `roofline` divides the bytes a decode
 step must read (all weights once, plus the cache of the live requests) by the step time.  Every step
-streams more bytes than the L2 holds, so nothing is flushed between timed iterations.
+streams more bytes than the L2 holds, so nothing is flushed between timed iterations.  The default run
+(1b) also times the decode of the 7b and 8b workloads, each in a child process, with their own numbers of
+steps: `points.decode_7b_b8`, `points.decode_8b_b64` and `other_workloads` (--no-other-workloads leaves
+them out).
 
 `--impl reference` runs the same workload through the unmodified reference (a CPU engine for one
 sequence at a time: it takes the sequences one after another) and prints the same line.
@@ -252,6 +255,21 @@ def measure_prefill(model, prompts, runs=5):
     return statistics.median(times)
 
 
+def other_workload(name: str, timeout: float = 240.0) -> dict:
+    """`python bench.py --shape NAME --only decode` in a child process; its short line, or why there is none."""
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--shape", name, "--only", "decode"]
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"no result within {timeout:.0f} s"}
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    if out.returncode != 0 or not lines:
+        tail = (out.stderr or out.stdout).strip().splitlines()[-1:] or [""]
+        return {"unavailable": f"exit code {out.returncode}: {tail[0][:200]}"}
+    d = json.loads(lines[-1])
+    return {k: d[k] for k in ("batch", "tok_s", "ms_per_step", "gb_s", "of_hbm_peak", "steps") if k in d}
+
+
 def flat_config(shape, cfg, layers_full, batch, steps, weights, kv_per_token, prompts):
     lens = [len(p) for p in prompts]
     lo, hi = shape["prompt_lengths"]
@@ -300,7 +318,7 @@ def run_ours(args):
         tps, ms_step, _, kernels = measure_decode(model, shape, batch, steps, args.warmup)
         held = measure_decode.last_held
         gbs = (weights + held * kv_per_token) / (ms_step / 1e3) / 1e9
-        print(json.dumps({"only": "decode", "shape": args.shape, "batch": batch, "tok_s": round(tps, 1),
+        print(json.dumps({"only": "decode", "shape": args.shape, "batch": batch, "steps": steps, "tok_s": round(tps, 1),
                           "ms_per_step": round(ms_step, 4), "kernels_per_step": kernels,
                           "tokens_held": int(held), "gb_s": round(gbs, 1), "of_hbm_peak": round(gbs / pk["hbm_gbs"], 3)}))
         return 0
@@ -332,6 +350,17 @@ def run_ours(args):
     pre_tokens = sum(map(len, pre_prompts))
     flops = prefill_flops(cfg, [len(p) for p in pre_prompts])
 
+    # the other two workloads of the benchmark, each in a process of its own (its own memory, and a
+    # failure there leaves this line whole): device-timed decode with its share of the HBM peak
+    others = {}
+    if args.shape == "1b" and not args.no_other_workloads and not args.layers:
+        del model
+        torch.cuda.empty_cache()
+        for other in ("7b", "8b"):
+            others[other] = other_workload(other)
+            if "tok_s" in others[other]:
+                points[f"decode_{other}_b{others[other]['batch']}"] = others[other]["tok_s"]
+
     step_bytes = weights + held_mean * kv_per_token
     achieved = step_bytes / (ms_step / 1e3) / 1e9
     from alpacca_b200.engine.decode import bucket_rows
@@ -356,6 +385,8 @@ def run_ours(args):
         "points": points,
         "clocks": clock_info,
     }
+    if others:
+        line["other_workloads"] = others
     print(json.dumps(line), flush=True)
     return 0
 
@@ -506,6 +537,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="measure one part only and print a short line (for profiling runs)")
+    ap.add_argument("--no-other-workloads", action="store_true",
+                    help="the default run also times the decode of the 7b and 8b workloads (in child processes, "
+                         "into `points` and `other_workloads`); this leaves them out")
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="with --only decode: equal prompts of this many tokens instead of the workload's")
     ap.add_argument("--prefill-tokens", type=int, default=0,
