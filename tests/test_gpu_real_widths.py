@@ -159,3 +159,36 @@ def test_generation_in_bfloat16_at_the_1b_widths(wide):
         rows = pl.logits(seq[:-1], list(range(len(prompts[b]) - 1, len(seq) - 1)))
         for row, t in zip(rows, res[b].token_ids):
             assert row[t] >= row.max() - 2 * logit_tolerances(row, "bfloat16")[0], (b, t, int(np.argmax(row)))
+
+
+def test_all_sixteen_layers_in_bfloat16_against_float32(tmp_path_factory):
+    """The whole Llama-3.2-1B shape, all 16 layers (the tests above run 2 of them against the plain
+    implementation, which would take minutes here): the bfloat16 engine against the 32-bit engine on the
+    SAME weights (a bfloat16 folder, widened exactly by the 32-bit load), a prompt in one step and tokens
+    one by one.  What differs is only the rounding of activations, through sixteen layers of residual
+    sums: it has to stay a small share of the logits' spread, and the 32-bit engine's greedy choice must
+    be among the bfloat16 engine's best within that error."""
+    from alpacca_b200.engine import Engine, StepEntry
+    from alpacca_b200.engine.loading import load_model_dir, write_random_model_dir
+    from helpers import logit_tolerances
+    cfg = dict(WIDTHS_1B, num_hidden_layers=16)
+    d = write_random_model_dir(tmp_path_factory.mktemp("full_1b") / "bf16", cfg, seed=23, dtype="bfloat16")
+    toks = tiny.prompt_tokens(cfg, 300, 3300)
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(load_model_dir(d, dtype=dtype, device="cuda", max_positions=512), max_tokens=64 * 8, max_slots=1)
+        slot = eng.alloc_slot()
+        rows = [eng.step([StepEntry(slot, toks[:290], [0, 100, 289])]).cpu().numpy()]
+        for p in range(290, 300):
+            rows.append(eng.step([StepEntry(slot, [toks[p]], [0])]).cpu().numpy())
+        got[dtype] = np.concatenate(rows)
+        eng.free_slot(slot)
+        del eng
+        import torch
+        torch.cuda.empty_cache()
+    ref, low = got["float32"].astype(np.float64), got["bfloat16"].astype(np.float64)
+    assert np.isfinite(low).all() and ref.std() > 0.3, "logits of order 1 are expected at these widths"
+    for i in range(ref.shape[0]):
+        check_logits(low[i], ref[i], "bfloat16", f"16 layers, row {i}, bfloat16 against float32")
+        best = int(np.argmax(ref[i]))
+        assert low[i][best] >= low[i].max() - 2 * logit_tolerances(ref[i], "bfloat16")[0]
