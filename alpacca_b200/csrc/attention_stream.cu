@@ -8,7 +8,7 @@
 // kernel is built to keep it streaming:
 //
 //   - a page of the cache (64 keys of one KV head, K and V) is one stage of a ring in shared memory.
-//     One thread (the producer) asks the TMA unit for whole pages, STAGES ahead of the warps that
+//     One thread (the producer) asks the TMA unit for whole pages, up to STAGES (2 to 12) ahead of the warps that
 //     use them: `cp.async.bulk.tensor` with the 128-byte swizzle, completion counted by an mbarrier
 //     per stage.  No thread spends instructions on addresses or waits on loads of its own;
 //   - four consumer warps take 16 keys of each page.  As in attention_mma.cu the KEYS are the 16 rows
@@ -164,8 +164,8 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ arrivals,
                         bf16* __restrict__ k_out, bf16* __restrict__ v_out, const int* __restrict__ block_table,
                         int table_width, const int* __restrict__ tok_seq, const int* __restrict__ kv_len,
-                        const int* __restrict__ row_order, int H, int K, float scale_log2, int window, int pages_per_cta, int n_chunks, int merge,
-                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_rot, int pairing,
+                        const int* __restrict__ row_order, int H, int K, float scale_log2, int window,
+                        int pages_per_cta, int n_chunks, int merge, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_rot, int pairing,
                         int fuse, int* __restrict__ status) {
   using Sm = StreamSmem<HD, STAGES>;
   constexpr int D = HD;
