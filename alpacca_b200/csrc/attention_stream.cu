@@ -165,8 +165,9 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         bf16* __restrict__ k_out, bf16* __restrict__ v_out, const int* __restrict__ block_table,
                         int table_width, const int* __restrict__ tok_seq, const int* __restrict__ kv_len,
                         const int* __restrict__ row_order, int H, int K, float scale_log2, int window,
-                        int pages_per_cta, int n_chunks, int merge, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_rot, int pairing,
-                        int fuse, int* __restrict__ status) {
+                        int pages_per_cta, int n_chunks, int merge, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t, int n_rot, int pairing, int fuse,
+                        int* __restrict__ status) {
   using Sm = StreamSmem<HD, STAGES>;
   constexpr int D = HD;
   extern __shared__ unsigned char smem_raw[];
