@@ -236,9 +236,11 @@ def measure_e2e(model, shape, batch, steps, seed=1):
 
 def measure_prefill(model, prompts, runs=5):
     """Median device time (ms) of one step that runs `prompts` whole."""
+    import numpy as np
     import torch
     from alpacca_b200.engine.step import StepEntry
     eng = model.engine
+    prompts = [np.asarray(p, dtype=np.int32) for p in prompts]     # token ids as arrays, as a tokenizer hands them over
     times = []
     for i in range(runs + 2):
         slots = [eng.alloc_slot() for _ in prompts]
