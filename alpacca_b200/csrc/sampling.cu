@@ -63,7 +63,9 @@ __device__ __forceinline__ unsigned int float_key(float x) {
 
 __device__ __forceinline__ unsigned long long weight_fx(float l, float m, float inv_t) {
   const float w = expf((l - m) * inv_t);               // in (0, 1]
-  return (unsigned long long)((double)w * (double)(1ull << W_SHIFT));
+  // w * 2^40 is exact in float (a shift of the exponent), so this is the truncation of the same real
+  // number that the double-precision product would give, without the slow double-precision units
+  return __float2ull_rz(w * 1099511627776.0f);
 }
 
 __device__ void philox4x32_10(unsigned int c0, unsigned int c1, unsigned int c2, unsigned int c3,
@@ -97,6 +99,10 @@ struct SampleShared {
   float max_v;
   int arg;
   int result;
+  // the segment (a warp's share of the vocabulary) that holds the drawn weight, with what lies before it
+  int seg0, seg1;
+  unsigned long long seg_w;
+  unsigned int seg_ties;
 };
 
 // block-wide exclusive scan of one 64-bit and one 32-bit value per thread; also the totals
@@ -326,7 +332,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   // (whole lines of memory per load), so "index order" inside a warp is (round, lane).  A tie's rank
   // in index order is the number of ties before it: the warps before (a scan of 32 counts), the
   // rounds before and the lanes before (a ballot).  The kept weight of the warps is scanned the same
-  // way; the warp whose share holds the target walks its segment once more to find the index.
+  // way; the segment whose share holds the target is then searched by the whole block.
   const int seg = (vocab + 31) / 32;
   const int s0 = min(vocab, warp * seg), s1 = min(vocab, s0 + seg);
   const unsigned int lanes_before = (1u << lane) - 1u;
@@ -378,26 +384,58 @@ sample_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   philox4x32_10((unsigned int)steps[row], 0u, (unsigned int)streams[row], 0u, seed_lo, seed_hi, &x0);
   const double u = (double)(x0 >> 8) * (1.0 / 16777216.0);
   const unsigned long long target = (unsigned long long)((double)w_total * u);
-  if (tid == 0) sh.result = sh.arg;     // fallback: the maximum (always kept)
+  if (tid == 0) { sh.result = sh.arg; sh.seg0 = -1; }     // fallback: the maximum (always kept)
   __syncthreads();
-  if (my_w > 0 && w_before <= target && target < w_before + my_w) {
-    // this warp's share holds the target: the first index at which the running weight exceeds it
-    unsigned long long acc = w_before;
-    unsigned int rank = ties_before;
-    for (int i0 = s0; i0 < s1; i0 += 32) {
-      const unsigned long long w = kept_weight(i0 + lane, rank);
-      unsigned long long incl = w;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
+  if (lane == 0 && my_w > 0 && w_before <= target && target < w_before + my_w) {
+    // this warp's segment holds the target; the whole block looks for the index in it
+    sh.seg0 = s0;
+    sh.seg1 = s1;
+    sh.seg_w = w_before;
+    sh.seg_ties = ties_before;
+  }
+  __syncthreads();
+  if (sh.seg0 >= 0) {
+    // every thread takes a few consecutive indices of the segment (a warp walking it alone, round
+    // after round, waits for one load per round: 126 round trips for a vocabulary of 128,256)
+    const int S0 = sh.seg0, S1 = sh.seg1;
+    const int chunk = (S1 - S0 + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int i0 = min(S1, S0 + tid * chunk), i1 = min(S1, i0 + chunk);
+    unsigned int rank0 = 0;
+    if (ties_limited) {
+      unsigned int mine = 0;
+      for (int i = i0; i < i1; ++i) mine += float_key(l[i]) == t_key;
+      unsigned long long we, wt;
+      unsigned int ct;
+      block_scan(0ull, mine, &we, &rank0, &wt, &ct, &sh);
+    }
+    rank0 += sh.seg_ties;
+    auto kept = [&](int i, unsigned int& rank) -> unsigned long long {
+      const float v = l[i];
+      const unsigned int key = float_key(v);
+      bool keep = true;
+      if (ties_limited) {
+        if (key > t_key) keep = true;
+        else if (key == t_key) keep = rank++ < c_ties;
+        else keep = false;
       }
-      const unsigned int hit = __ballot_sync(0xffffffffu, w > 0 && acc + incl > target);
-      if (hit) {
-        if (lane == __ffs(hit) - 1) sh.result = i0 + lane;
-        break;
+      return keep ? weight_fx(v, m, inv_t) : 0ull;
+    };
+    unsigned long long mine_w = 0;
+    {
+      unsigned int rank = rank0;
+      for (int i = i0; i < i1; ++i) mine_w += kept(i, rank);
+    }
+    unsigned long long before, total;
+    unsigned int ce, ct;
+    block_scan(mine_w, 0u, &before, &ce, &total, &ct, &sh);
+    before += sh.seg_w;
+    if (mine_w > 0 && before <= target && target < before + mine_w) {
+      unsigned long long acc = before;
+      unsigned int rank = rank0;
+      for (int i = i0; i < i1; ++i) {
+        acc += kept(i, rank);
+        if (acc > target) { sh.result = i; break; }
       }
-      acc += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
   __syncthreads();
