@@ -392,15 +392,26 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     if (chunk == 0 && ok) {
       for (int idx = tid; idx < n_heads * D; idx += AS_THREADS) {
         const int r = idx / D, d = idx - r * D;
+        // a cluster has at most 8 chunks: their values are fetched together, then added in chunk order
+        float mc[8], lc[8], oc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = first_chunk + j;
+          const bool in = c <= last_chunk;
+          const float* ml = cluster.map_shared_rank(cta_ml, in ? c : first_chunk);
+          mc[j] = in ? ml[r * 2] : -INFINITY;
+          lc[j] = in ? ml[r * 2 + 1] : 0.f;
+          oc[j] = in ? cluster.map_shared_rank(cta_o, in ? c : first_chunk)[r * D + d] : 0.f;
+        }
         float m = -INFINITY;
-        for (int c = first_chunk; c <= last_chunk; ++c) m = fmaxf(m, cluster.map_shared_rank(cta_ml, c)[r * 2]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, mc[j]);
         float l = 0.f, o = 0.f;
-        for (int c = first_chunk; c <= last_chunk; ++c) {
-          const float* ml = cluster.map_shared_rank(cta_ml, c);
-          const float mc = ml[r * 2];
-          const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - m);
-          l += ml[r * 2 + 1] * f;
-          o += cluster.map_shared_rank(cta_o, c)[r * D + d] * f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float f = (mc[j] == -INFINITY) ? 0.f : exp2f(mc[j] - m);
+          l += lc[j] * f;
+          o += oc[j] * f;
         }
         out[((size_t)tok * H + kh * G + rt * 8 + r) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
       }
@@ -427,20 +438,42 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = tid; idx < n_heads * D; idx += AS_THREADS) {
-    const int r = idx / D, d = idx - r * D;
+  // Eight chunks at a time, their loads issued together (a loop that fetched chunk after chunk took the
+  // memory's latency once per chunk: 0.45 us each, 10 us for 22 chunks); always in chunk order.  A
+  // thread owns four neighbouring elements of a head's output.
+  for (int idx = tid; idx < n_heads * (D / 4); idx += AS_THREADS) {
+    const int r = idx / (D / 4), d = (idx - r * (D / 4)) * 4;
     const int h = kh * G + rt * 8 + r;
     const size_t at = ((size_t)tok * H + h) * n_chunks;
-    float m = -INFINITY;
-    for (int c = first_chunk; c <= last_chunk; ++c) m = fmaxf(m, __ldcg(part_ml + (at + c) * 2));
-    float l = 0.f, o = 0.f;
-    for (int c = first_chunk; c <= last_chunk; ++c) {
-      const float mc = __ldcg(part_ml + (at + c) * 2);
-      const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - m);
-      l += __ldcg(part_ml + (at + c) * 2 + 1) * f;
-      o += __ldcg(part_o + (at + c) * D + d) * f;
+    float m = -INFINITY, l = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = first_chunk; c0 <= last_chunk; c0 += 8) {
+      float2 ml[8];
+      float4 oc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = c0 + j <= last_chunk;
+        ml[j] = in ? __ldcg(reinterpret_cast<const float2*>(part_ml) + at + c0 + j) : make_float2(-INFINITY, 0.f);
+        oc[j] = in ? __ldcg(reinterpret_cast<const float4*>(part_o + (at + c0 + j) * D + d))
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float top = m;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) top = fmaxf(top, ml[j].x);
+      const float keep = (m == -INFINITY) ? 0.f : exp2f(m - top);
+      l *= keep;
+      o.x *= keep; o.y *= keep; o.z *= keep; o.w *= keep;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = (ml[j].x == -INFINITY) ? 0.f : exp2f(ml[j].x - top);
+        l += ml[j].y * f;
+        o.x += oc[j].x * f; o.y += oc[j].y * f; o.z += oc[j].z * f; o.w += oc[j].w * f;
+      }
+      m = top;
     }
-    out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    bf16* dst = out + ((size_t)tok * H + h) * D + d;
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(l > 0.f ? o.x / l : 0.f, l > 0.f ? o.y / l : 0.f);
+    *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(l > 0.f ? o.z / l : 0.f, l > 0.f ? o.w / l : 0.f);
   }
 }
 

@@ -302,6 +302,8 @@ def run_ours(args):
     shape = dict(SHAPES[args.shape])
     if args.only == "decode" and args.prompt_len:
         shape["prompt_lengths"] = (args.prompt_len, args.prompt_len)
+        # room for the prompt, the warm-up steps and the timed steps in every slot
+        shape["context"] = max(shape["context"], args.prompt_len + max(args.warmup, 3) + (args.steps or shape["steps"]) + 1)
     if args.only == "prefill" and args.prefill_tokens:
         shape["prefill_tokens"] = args.prefill_tokens
         shape["context"] = max(shape["context"], args.prefill_tokens)
