@@ -530,8 +530,24 @@ def attention_stream(qkv, out, cache, ctx, H, K, D, scale, window=0, rot=None, f
     return out
 
 
-STREAM_DECODE = True             # decode steps that read much cache: the streamed kernel (head sizes 64, 128)
-STREAM_MIN_BYTES = 40e6          # ... from this many bytes of cache per layer (by the block table's width)
+STREAM_DECODE = True             # decode steps may take the streamed kernel (head sizes 64, 128)
+STREAM_MIN_BYTES = None          # None: where it was measured to win (`_stream_pays`); a number: from that many
+                                 # bytes of cache per layer, by the block table's width (0 always, inf never)
+
+
+def _stream_pays(pairs: int, width: int, D: int) -> bool:
+    """Whether the streamed decode attention beats the other decode kernel for `pairs` (sequence, KV head)
+    pairs over block tables `width` pages wide.  Measured on a B200, each kernel with its own plan, 1 to 32
+    sequences of 500 to 16,000 tokens, 8 and 32 KV heads (microseconds per layer, streamed / other): head
+    size 128: it wins everywhere (one sequence of 500 tokens 6.1 / 7.8, 8 of 1,000 11.0 / 15.6, 2 of 16,000
+    27 / 70); head size 64: it wins from tables of 24 pages (8 sequences of 2,000 tokens 11.0 / 14.0, 2 of 16,000
+    16.8 / 33.2; a tie to 12 % worse for one or two sequences of 2,000 to 4,000), from 16 pages for up to
+    four sequences (one of 1,000 tokens 5.4 / 7.3, four 6.7 / 8.1; eight are a tie at 1,000 tokens and
+    lose at 800), and loses below (8 of 500 tokens 6.6 / 4.9, one 4.9 / 4.6) unless there are hundreds of
+    pairs (32 sequences of 500: 9.0 / 10.1)."""
+    if STREAM_MIN_BYTES is not None:
+        return pairs * width * 64 * D * 4 >= STREAM_MIN_BYTES
+    return D == 128 or width >= 24 or (width >= 16 and pairs <= 32) or pairs * width * 64 * D * 4 >= 30e6
 
 
 def _stream_plan(rows: int, H: int, K: int, D: int, width: int, sms: int):
@@ -540,14 +556,14 @@ def _stream_plan(rows: int, H: int, K: int, D: int, width: int, sms: int):
     other decode kernel at its best plan (microseconds per layer): 64 sequences of 530 tokens, 8 KV heads
     of 64: 15.4 against 17.5; of 2,000 tokens: 48.4 against 55.3; 64 sequences of 128 to 2,048 tokens, 8
     KV heads of 128: 63.1 against 100.9; 8 sequences of 16 to 1,024 tokens, 32 KV heads of 128: 17.9
-    against 31.6; 8 sequences of 3,800 tokens, 8 heads of 64: 15.5 against 18.4.  It loses where little
-    is read (8 sequences of 640 tokens: 6.9 against 5.1; one sequence: 5.4 against 4.75), hence the
-    threshold.  One CTA per (sequence, KV head) is best once there are more of those than processors;
+    against 31.6; 8 sequences of 3,800 tokens, 8 heads of 64: 15.5 against 18.4.  Where little is read it loses
+    at head size 64 (8 sequences of 640 tokens: 6.9 against 5.1; one sequence: 5.4 against 4.75), hence
+    `_stream_pays`.  One CTA per (sequence, KV head) is best once there are more of those than processors;
     fewer are cut into chunks that a cluster merges; many CTAs of few pages take the short ring."""
     if not STREAM_DECODE or D not in (64, 128):
         return None
     pairs = rows * K * -(-(H // K) // 8)
-    if pairs * width * 64 * D * 4 < STREAM_MIN_BYTES:
+    if not _stream_pays(pairs, width, D):
         return None
     want = -(-3 * sms // (2 * pairs))
     if want > DECODE_MAX_CLUSTER and width >= 8 * DECODE_MAX_CLUSTER:

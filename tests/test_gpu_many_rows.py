@@ -40,7 +40,7 @@ def test_logits_of_every_decode_step(model_dirs, name, n, dtype, monkeypatch):
     """The prompts in one step, then four single-token steps through `Engine.step` and four replayed
     from the graph (which feeds on its own sampled tokens): the logits of every step against the
     plain implementation's for the sequence as it stands.  "streamed": the decode attention that
-    streams the cache, which otherwise only takes steps that read tens of megabytes, takes every step.
+    streams the cache takes every step; without it the other decode kernel does.
     ("C" has five KV heads: 64 sequences are 320 (sequence, KV head) pairs, more than the device has
     processors, so the other decode kernel takes its small CTAs, several per processor.)"""
     from alpacca_b200 import ops
@@ -55,6 +55,7 @@ def test_logits_of_every_decode_step(model_dirs, name, n, dtype, monkeypatch):
         monkeypatch.setattr(ops, "attention_stream", lambda *a, **k: (launched.append(1), real(*a, **k))[1])
     else:
         launched = None
+        monkeypatch.setattr(ops, "STREAM_MIN_BYTES", float("inf"))     # the other decode kernel takes every step
     from alpacca_b200.engine.step import StepEntry
     from alpacca_b200.sampling import DeviceSampler, SamplerParams
     d = model_dirs[(name, dtype)]

@@ -112,10 +112,10 @@ def test_whole_then_one_by_one_then_a_batch(wide, dtype, monkeypatch):
     # 2. its last 8 tokens one by one, on the cache that the long step left; every other one with the
     # decode attention that streams the cache (which by itself only takes steps that read more)
     for p in range(long_len - 8, long_len):
-        monkeypatch.setattr(ops, "STREAM_MIN_BYTES", 0 if p % 2 else 40e6)
+        monkeypatch.setattr(ops, "STREAM_MIN_BYTES", 0 if p % 2 else float("inf"))
         got = eng.step([StepEntry(slot, [toks[p]], [0])]).cpu().numpy()
         check(got, pl.logits(toks, [p]), f"token {p} fed alone")
-    monkeypatch.setattr(ops, "STREAM_MIN_BYTES", 40e6)
+    monkeypatch.setattr(ops, "STREAM_MIN_BYTES", None)
     eng.free_slot(slot)
     # 3. three unequal prompts in one step (slots and pages used again), then two steps of one token each
     seqs = [tiny.prompt_tokens(cfg, n, 3100 + i) for i, n in enumerate((300, 131, 40))]
