@@ -312,6 +312,8 @@ def run_ours(args):
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     batch = args.batch or shape["batch"]
+    if args.only == "prefill" and args.prefill_tokens and not args.batch:
+        batch = 1           # one prompt: the cache is sized for it alone
     steps = args.steps or shape["steps"]
     biggest = max([batch, *shape["points"]]) if args.only == "all" else batch
     model = Model.random(cfg, seed=0, n_ctx=shape["context"], dtype="bfloat16", max_batch=biggest)
