@@ -505,6 +505,199 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 }
 
 // ---------------------------------------------------------------------------
+// The persistent form on pairs of processors: a cluster of two CTAs computes tiles of 256 x 256 with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of X and HALF of the tile's 256 rows of W
+// (32 KB a stage instead of 48: an MMA reads the other half from the partner's shared memory), and
+// holds its 128 rows of the accumulator in its own TMEM.  CTA 0 of the pair (the leader) issues all
+// MMAs; the copies of both CTAs report to the leader's `full` barriers, the leader's commits arrive at
+// the `empty` and `acc_full` barriers of both, and the tails of both report to the leader's `acc_empty`.
+// What it buys: the plain persistent form needs 96 bytes a cycle from the L2 per processor to keep
+// its MMAs fed, this one 64.
+// ---------------------------------------------------------------------------
+#define T2_STAGES 6
+#define T2_A_BYTES (TC_BM * TC_BK * 2)
+#define T2_B_BYTES (128 * TC_BK * 2)
+#define T2_STAGE_BYTES (T2_A_BYTES + T2_B_BYTES)
+#define T2_SMEM (T2_STAGES * T2_STAGE_BYTES + 1024 + 256)
+#define T2_BAND 8            // pair tiles (256 rows) per band, as TP_BAND
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the address of `local` (an address in this CTA's shared memory) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t local, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a copy into this CTA's shared memory whose bytes are counted by a barrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// arrives at the barrier at this offset in both CTAs of the pair when the MMAs before it are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_addr(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void t2_tile_origin(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+  const int per_band = T2_BAND * tiles_n;
+  const int band = tile / per_band, within = tile - band * per_band;
+  const int rows = min(T2_BAND, tiles_m - band * T2_BAND);
+  const int col = within / rows;
+  m0 = (band * T2_BAND + (within - col * rows)) * (2 * TC_BM);
+  n0 = col * TP_BN;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    void* __restrict__ Y, const float* __restrict__ bias, int* __restrict__ status, int M, int N,
+                    int K, int ldy, int tiles_m, int n_tiles) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + T2_STAGES * T2_STAGE_BYTES);
+  uint64_t* empty = full + T2_STAGES;
+  uint64_t* acc_full = empty + T2_STAGES;      // [2] the MMAs of a tile are done (arrives in both CTAs)
+  uint64_t* acc_empty = acc_full + 2;          // [2] leader's: the tails of both CTAs have read the buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  const int tiles_n = n_tiles / tiles_m;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T2_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();          // the partner's barriers are initialised before anything arrives at them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      const int first = pair;
+      const int early = first < n_tiles ? min(nkb, T2_STAGES) : 0;
+      int n0_first = 0, m0_first = 0;
+      if (first < n_tiles) t2_tile_origin(first, tiles_m, tiles_n, m0_first, n0_first);
+      // weights of the first stages before the wait (they do not depend on the kernel before)
+      for (int i = 0; i < early; ++i) {
+        if (leader) mbar_expect_tx(full + i, 2 * T2_STAGE_BYTES);
+        tma_load_2d_pair(base + i * T2_STAGE_BYTES + T2_A_BYTES, &map_w, i * TC_BK, n0_first + (int)rank * 128,
+                         cluster_addr(smem_addr(full + i), 0));
+      }
+      pdl_wait();
+      pdl_trigger();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d_pair(base + i * T2_STAGE_BYTES, &map_x, i * TC_BK, m0_first + (int)rank * TC_BM,
+                         cluster_addr(smem_addr(full + i), 0));
+      for (int tile = first; tile < n_tiles && ok; tile += n_pairs) {
+        int m0, n0;
+        t2_tile_origin(tile, tiles_m, tiles_n, m0, n0);
+        for (int kb = (tile == first ? early : 0); kb < nkb; ++kb) {
+          const int i = it + kb;
+          const int s = i % T2_STAGES;
+          if (i >= T2_STAGES && !mbar_wait(empty + s, ((i / T2_STAGES) - 1) & 1)) { atomicExch(status, 31); ok = false; break; }
+          if (leader) mbar_expect_tx(full + s, 2 * T2_STAGE_BYTES);
+          const uint32_t bar = cluster_addr(smem_addr(full + s), 0);
+          tma_load_2d_pair(base + s * T2_STAGE_BYTES + T2_A_BYTES, &map_w, kb * TC_BK, n0 + (int)rank * 128, bar);
+          tma_load_2d_pair(base + s * T2_STAGE_BYTES, &map_x, kb * TC_BK, m0 + (int)rank * TC_BM, bar);
+        }
+        it += nkb;
+      }
+    } else {
+      pdl_wait();
+    }
+  } else if (warp == 1) {
+    pdl_wait();
+    if (lane == 0 && leader) {
+      // M = 256 (128 rows in each CTA), N = 256
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TP_BN >> 3) << 17) |
+                                 ((uint32_t)((2 * TC_BM) >> 4) << 24);
+      int it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++lt) {
+        const int buf = lt & 1;
+        if (lt >= 2 && !mbar_wait(acc_empty + buf, ((lt >> 1) - 1) & 1)) { atomicExch(status, 32); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem + (uint32_t)buf * TP_BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % T2_STAGES;
+          if (!mbar_wait(full + s, (it / T2_STAGES) & 1)) { atomicExch(status, 33); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_addr(base + s * T2_STAGE_BYTES), sb = sa + T2_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)
+            umma_bf16_pair(acc, umma_desc(sa + k * 32), umma_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(empty + s);
+        }
+        if (ok) umma_commit_pair(acc_full + buf);
+      }
+    }
+  } else {
+    pdl_wait();
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int lt = 0;
+    bool ok = true;
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++lt) {
+      const int buf = lt & 1;
+      int m0, n0;
+      t2_tile_origin(tile, tiles_m, tiles_n, m0, n0);
+      ok = mbar_wait(acc_full + buf, (lt >> 1) & 1);
+      if (!ok) atomicExch(status, 34);
+      ok = __all_sync(0xffffffffu, ok);      // tcgen05.ld below is warp-wide
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c0 = 0; c0 < TP_BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * TP_BN + c0, v);
+        tail16<EPI, false>(v, m0 + (int)rank * TC_BM + row, n0 + c0, M, N, bias, Y, ldy, lane);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(cluster_addr(smem_addr(acc_empty + buf), 0));
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();          // neither CTA gives its TMEM back, or leaves, while the other still works
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+  }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -642,6 +835,57 @@ AB_API int ab_gemm_tc_persistent(const void* X, const void* W, const float* bias
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
     e = ab_launch(gemm_tc_persistent_kernel<E>, dim3(grid), dim3(TC_THREADS), (size_t)TP_SMEM, stream, mx, mw, Y,  \
                   bias, status, M, N, K, ldy, tiles_m, n_tiles);                                                   \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
+    return ab_launch_status();                                                                                     \
+  }
+  switch (epilogue_kind) {
+    case EPI_STORE_BF16: AB_GO(EPI_STORE_BF16)
+    case EPI_STORE_F32: AB_GO(EPI_STORE_F32)
+    case EPI_SWIGLU_BF16: AB_GO(EPI_SWIGLU_BF16)
+  }
+#undef AB_GO
+  return AB_BAD_ARG;
+}
+
+// The persistent form on pairs of processors (tiles of 256 x 256, tcgen05.mma.cta_group::2).
+AB_API int ab_gemm_tc_pair(const void* X, const void* W, const float* bias, void* Y, int M, int N, int K,
+                           int ldy, int epilogue_kind, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return AB_OK;
+  if (K <= 0 || (K % 8)) return AB_BAD_ARG;
+  if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  int* status = status_word();
+  if (!status) return AB_BAD_ARG;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, X, M, K, TC_BM)) return AB_BAD_ARG;
+  if (!make_map(&mw, W, N, K, 128)) return AB_BAD_ARG;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles_m = (M + 2 * TC_BM - 1) / (2 * TC_BM), tiles_n = (N + TP_BN - 1) / TP_BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int pairs = n_tiles < sms / 2 ? n_tiles : sms / 2;
+#define AB_GO(E)                                                                                                   \
+  {                                                                                                                \
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM); \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
+    cudaLaunchConfig_t cfg = {};                                                                                   \
+    cfg.gridDim = dim3(2 * pairs);                                                                                 \
+    cfg.blockDim = dim3(TC_THREADS);                                                                               \
+    cfg.dynamicSmemBytes = (size_t)T2_SMEM;                                                                        \
+    cfg.stream = stream;                                                                                           \
+    cudaLaunchAttribute attr[2];                                                                                   \
+    attr[0].id = cudaLaunchAttributeClusterDimension;                                                              \
+    attr[0].val.clusterDim.x = 2;                                                                                  \
+    attr[0].val.clusterDim.y = 1;                                                                                  \
+    attr[0].val.clusterDim.z = 1;                                                                                  \
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                               \
+    attr[1].val.programmaticStreamSerializationAllowed = 1;                                                        \
+    cfg.attrs = attr;                                                                                              \
+    cfg.numAttrs = (ab_pdl_enabled() && !ab_pdl_held) ? 2 : 1;                                                     \
+    e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<E>, mx, mw, Y, bias, status, M, N, K, ldy, tiles_m, n_tiles); \
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
     return ab_launch_status();                                                                                     \
   }

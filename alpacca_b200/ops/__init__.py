@@ -786,7 +786,8 @@ def decode_advance(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, 
         int(window), _p(history), _p(counter), hist_len, n_rows, _stream()), "decode_advance")
 
 
-def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None, slices=None, persistent=True):
+def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None, slices=None, persistent=True,
+            pair=None):
     """out[:n] = x[:n] @ w^T (+ bias) on the tcgen05 tensor cores (TMA-fed, TMEM accumulators).
 
     x [M,K], w [N,K] bfloat16; out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row
@@ -794,7 +795,8 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
     128-row side of the MMA (the batch, up to 256 rows, becomes the columns): the shape for decode
     steps.  `bn` is the MMA's column count per tile, `slices` the number of K slices.  Without `swap`,
     256-wide tiles and one slice run as the persistent kernel (one CTA per SM walks the tiles) unless
-    `persistent` is off.
+    `persistent` is off; `pair` chooses its form on pairs of processors (tiles of 256 x 256,
+    `tcgen05.mma.cta_group::2`; default: `TC_PAIR`).
     """
     _cuda(x, w, out, bias)
     n = x.shape[0] if n_rows is None else n_rows
@@ -821,8 +823,9 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
     _tc_unchecked["gemm_tc"] = True
     if not swap and bn == 256 and slices in (None, 1) and persistent:
         # many rows: the persistent form (tails under the next tile's main loop)
-        _check(_lib("gemm_tc").ab_gemm_tc_persistent(_p(x), _p(w), _p(bias), _p(out), n, N, K, out.shape[-1], epi,
-                                                     _stream()), "gemm_tc")
+        lib = _lib("gemm_tc")
+        run = lib.ab_gemm_tc_pair if (TC_PAIR if pair is None else pair) else lib.ab_gemm_tc_persistent
+        _check(run(_p(x), _p(w), _p(bias), _p(out), n, N, K, out.shape[-1], epi, _stream()), "gemm_tc")
         return out
     rows_a, rows_b = (N, n) if swap else (n, N)
     tiles = -(-rows_a // 128) * -(-rows_b // bn)
@@ -836,6 +839,14 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
                                       out.shape[-1], epi, 1 if swap else 0, bn, slices, _stream()), "gemm_tc")
     return out
 
+
+# The persistent product on pairs of processors (`tcgen05.mma.cta_group::2`, see `gemm_tc`).  Measured on a
+# B200 against the form with one processor per tile: gate|up with the activation 2048 x 16384 x 2048 101.6
+# against 100.9 us, 4797 x 22016 x 4096 587 against 602, plain 16384 x 4096 x 14336 1,307 against 1,412 us
+# (library 1,258); whole prompt steps: 1B shape 2,048 tokens 4.35 ms either way, the 7B workload's 4,797 tokens
+# 55.0 against 56.2 ms, the 8B workload's 76,771 tokens 1.00 against 1.07 s (it moves a third less through the
+# shared memory, which under the power cap is worth more than the kernel alone shows).
+TC_PAIR = True
 
 # kernels that wait on barriers with a limit, launched since the last check
 _tc_unchecked = {"gemm_tc": False, "attention_tc": False, "attention_stream": False}

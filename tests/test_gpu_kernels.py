@@ -577,22 +577,25 @@ def test_attention_decode_many_sequences(H, K, D, B):
             close(out[b].view(1, H, D), want, "bfloat16", f"sequence {b} of {lengths[b]}, window {window}")
 
 
-@pytest.mark.parametrize("M,N,K", [(2500, 2100, 328), (4000, 3000, 200), (130, 300, 4104)])
-def test_gemm_tc_persistent(M, N, K):
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("M,N,K", [(2500, 2100, 328), (4000, 3000, 200), (130, 300, 4104), (256, 256, 64), (20000, 700, 520)])
+def test_gemm_tc_persistent(M, N, K, pair):
     """The persistent form of the tcgen05 product: more tiles than processors (a CTA walks several,
-    both accumulator buffers in turn), ragged edges in every direction, both output types."""
+    both accumulator buffers in turn), ragged edges in every direction, both output types; `pair`: on
+    pairs of processors (tiles of 256 x 256 by `tcgen05.mma.cta_group::2`)."""
     from alpacca_b200 import ops
     x, w, bias = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.1), rnd(N, seed=3)
     want = x.double() @ w.double().T + bias.double()
     for dt, tol in ((torch.float32, "float32"), (torch.bfloat16, "bfloat16")):
         out = torch.full((M, N), 9.0, dtype=dt, device="cuda")
-        ops.gemm_tc(x, w, out, bias=bias, swap=False, bn=256, slices=1)
+        ops.gemm_tc(x, w, out, bias=bias, swap=False, bn=256, slices=1, pair=pair)
         close(out, want, tol, f"persistent gemm_tc {dt}")
     assert ops.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,F,K", [(3000, 1304, 264), (1024, 512, 2048)])
-def test_gemm_tc_persistent_swiglu(M, F, K):
+def test_gemm_tc_persistent_swiglu(M, F, K, pair):
     from alpacca_b200 import ops
     x = rnd(M, K, dtype=torch.bfloat16, seed=1)
     gate, up = rnd(F, K, dtype=torch.bfloat16, seed=2, scale=K ** -0.5), rnd(F, K, dtype=torch.bfloat16, seed=3, scale=K ** -0.5)
@@ -602,6 +605,6 @@ def test_gemm_tc_persistent_swiglu(M, F, K):
     g = x.double() @ gate.double().T + bg.double()
     u = x.double() @ up.double().T + bu.double()
     out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
-    ops.gemm_tc(x, w, out, bias=bias, swiglu=True, swap=False)
+    ops.gemm_tc(x, w, out, bias=bias, swiglu=True, swap=False, pair=pair)
     close(out, g / (1 + torch.exp(-g)) * u, "bfloat16", "persistent swiglu epilogue")
     assert ops.gemm_tc_status() == 0
