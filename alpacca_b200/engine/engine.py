@@ -5,8 +5,16 @@ slots hold, as one batch, and returns the logits at the wanted places.  Prompts
 of unequal lengths go in one step; afterwards one token per sequence.  The
 reference's counterparts are `prefill` / `forward_batch` / `forward`
 (alpacca/model.py:610-641, :469-518, :439-445), for its single sequence.
+
+A prompt step whose shape was seen before (the same numbers of new and held tokens of every sequence,
+the same wanted places per sequence) is replayed from a CUDA graph: the second step of a shape is run
+launch by launch on index arrays that stay where they are and is captured afterwards, later ones copy
+their token ids, slots, pages and wanted places into those arrays and replay.  A step of 2,048 tokens
+of the 1B shape takes 3.8 ms of device time and 4.4 ms when the host issues its 130 launches one by one.
 """
 from __future__ import annotations
+
+from collections import OrderedDict
 
 import numpy as np
 import torch
@@ -35,6 +43,10 @@ class Engine:
                                    opts.dtype, self.device)
         self.vocab_size = model.spec.vocab_size
         self._builder = ContextBuilder(self.device)
+        # prompt steps replayed from graphs: shape -> times seen, shape -> (context, graph, logits)
+        self.prompt_graphs = self.device.type == "cuda" and model.all_capturable()
+        self._shapes_seen: dict = {}
+        self._graphs: OrderedDict = OrderedDict()
 
     # -- slots -------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -97,13 +109,59 @@ class Engine:
         lengths = [self.cache.length(e.slot) for e in entries]
         return self._builder.build(entries, lengths, self.cache, arrays)
 
+    PROMPT_GRAPH_MAX_TOKENS = 8192      # longer steps are bound by the device, not by the host that issues them
+    PROMPT_GRAPHS_KEPT = 8
+
+    def _shape_of(self, entries, lengths):
+        """What decides every launch of a prompt step (the rest - token ids, slots, pages, wanted places -
+        is data in device memory); None for steps that are not replayed from graphs."""
+        q_lens = tuple(len(e.tokens) for e in entries)
+        if not self.prompt_graphs or max(q_lens) == 1 or sum(q_lens) > self.PROMPT_GRAPH_MAX_TOKENS:
+            return None
+        every = all(len(e.want) == q and all(w == i for i, w in enumerate(e.want)) for e, q in zip(entries, q_lens))
+        slots = [e.slot for e in entries]
+        widths = tuple(self.cache.table_width(g, slots) for g in range(len(self.cache.kv_groups)))
+        return q_lens, tuple(lengths), tuple(len(e.want) for e in entries), every, widths
+
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Runs one step; returns float32 logits [number of wanted places, vocab] on the device,
         in the order of the entries and of their `want` lists."""
-        ctx = self.prepare(entries)
-        logits = self.model.forward(ctx, self.cache)
-        self.cache.commit([(e.slot, len(e.tokens)) for e in entries])
+        arrays = self._check(entries)
+        requests = [(e.slot, len(e.tokens)) for e in entries]
+        self.cache.reserve(requests)          # raises CacheFull before anything is launched
+        lengths = [self.cache.length(e.slot) for e in entries]
+        shape = self._shape_of(entries, lengths)
+        held = self._graphs.get(shape) if shape is not None else None
+        capture = None
+        if held is not None:
+            ctx, graph, logits = held
+            self._graphs.move_to_end(shape)
+            self._builder.build(entries, lengths, self.cache, arrays, into=ctx.buffer)
+            graph.replay()
+            logits = logits.clone()           # the graph's own memory is written again by its next replay
+        else:
+            ctx = self._builder.build(entries, lengths, self.cache, arrays)
+            logits = self.model.forward(ctx, self.cache)
+            if shape is not None:
+                seen = self._shapes_seen[shape] = self._shapes_seen.get(shape, 0) + 1
+                if seen == 2:
+                    capture = ctx
+        self.cache.commit(requests)
+        if capture is not None:
+            self._capture(shape, capture)
         return logits
+
+    def _capture(self, shape, ctx) -> None:
+        """Captures the step that was just issued with `ctx` (whose plans, made on the host during that run,
+        stay with it) for later steps of the same shape.  Nothing runs during the capture."""
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.cache)
+        self._graphs[shape] = (ctx, graph, logits)
+        while len(self._graphs) > self.PROMPT_GRAPHS_KEPT:
+            self._graphs.popitem(last=False)
+        if len(self._shapes_seen) > 4096:
+            self._shapes_seen.clear()
 
     def describe(self) -> str:
         return self.cache.describe()

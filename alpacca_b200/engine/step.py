@@ -43,6 +43,7 @@ class StepContext:
     row_order: torch.Tensor = None   # int32 [n_seqs], decode steps: the batch rows, longest sequence first
                                      # (kernels that give a row to a CTA start the long rows first)
     extras: dict = field(default_factory=dict)   # per-step plans of kernels (tile lists and the like)
+    buffer: torch.Tensor = None      # the one device buffer that all the index arrays above are views of
 
 
 def _pad4(n: int) -> int:
@@ -74,7 +75,9 @@ class ContextBuilder:
         self._slot = i
         return buf
 
-    def build(self, entries, lengths, cache, token_arrays=None) -> StepContext:
+    def build(self, entries, lengths, cache, token_arrays=None, into: torch.Tensor | None = None) -> StepContext:
+        """`into`: the `buffer` of a context built earlier for a step of the same shape (the same numbers of
+        tokens, sequences, wanted places and pages): the arrays are written there instead of into new memory."""
         B = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
@@ -108,7 +111,12 @@ class ContextBuilder:
         i_order = 7 + len(widths)
         if decode:
             host[offs[i_order]:offs[i_order] + B] = np.argsort(-kv, kind="stable")
-        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        if into is not None:
+            if into.numel() != total:
+                raise ValueError(f"a step of another shape than the buffer's ({total} against {into.numel()} entries)")
+            dev = into
+        else:
+            dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(stage[:total], non_blocking=True)
         if self.pinned:
             ev = torch.cuda.Event()
@@ -118,7 +126,7 @@ class ContextBuilder:
         def part(i, n):
             return dev[offs[i]:offs[i] + n]
         return StepContext(
-            n_tokens=T, n_seqs=B, n_want=n_want, is_decode=decode, row_order=part(i_order, B) if decode else None,
+            buffer=dev, n_tokens=T, n_seqs=B, n_want=n_want, is_decode=decode, row_order=part(i_order, B) if decode else None,
             max_q_len=max(q_lens), max_kv_len=int(kv.max()),
             tokens=part(0, T), tok_seq=part(1, T), tok_pos=part(2, T), cu_q=part(3, B + 1),
             kv_len=part(4, B), slots=part(5, B), want_rows=part(6, n_want),
