@@ -222,12 +222,16 @@ class SequenceCache:
     def fill_block_table(self, group: int, slots, out, width: int) -> None:
         """Writes the page lists of `slots` into `out` (a host int32 tensor [len(slots), width])."""
         g = self.kv_groups[group]
-        out.zero_()
+        table = out.numpy()         # the same memory; filling it row by row through torch costs 10 us a row
+        table[:] = 0
         for b, s in enumerate(slots):
             if s < 0:
                 continue
             pl = g.page_lists[s]
-            out[b, :len(pl)] = torch.tensor([max(p, 0) for p in pl], dtype=torch.int32)
+            if pl:
+                table[b, :len(pl)] = pl
+                if g.spec.window:           # pages that a window has given back are marked -1 in the list
+                    table[b, :len(pl)].clip(0, None, out=table[b, :len(pl)])
 
     def entry_view(self, entry: int, block_tables) -> KVLayerView | StateLayerView | None:
         place = self.entry_place[entry]

@@ -77,7 +77,8 @@ class ContextBuilder:
 
     def build(self, entries, lengths, cache, token_arrays=None, into: torch.Tensor | None = None) -> StepContext:
         """`into`: the `buffer` of a context built earlier for a step of the same shape (the same numbers of
-        tokens, sequences, wanted places and pages): the arrays are written there instead of into new memory."""
+        tokens, sequences, wanted places and pages): the arrays are written there instead of into new memory,
+        and nothing is returned (that context's views see them)."""
         B = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
@@ -122,6 +123,8 @@ class ContextBuilder:
             ev = torch.cuda.Event()
             ev.record()
             self._events[self._slot] = ev
+        if into is not None:
+            return None         # the context that owns `into` has its views already
 
         def part(i, n):
             return dev[offs[i]:offs[i] + n]
