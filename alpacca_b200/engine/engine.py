@@ -116,7 +116,8 @@ class Engine:
         """What decides every launch of a prompt step (the rest - token ids, slots, pages, wanted places -
         is data in device memory); None for steps that are not replayed from graphs."""
         q_lens = tuple(len(e.tokens) for e in entries)
-        if not self.prompt_graphs or max(q_lens) == 1 or sum(q_lens) > self.PROMPT_GRAPH_MAX_TOKENS:
+        if (not self.prompt_graphs or max(q_lens) == 1 or sum(q_lens) > self.PROMPT_GRAPH_MAX_TOKENS
+                or ops.timing()):
             return None
         every = all(len(e.want) == q and all(w == i for i, w in enumerate(e.want)) for e, q in zip(entries, q_lens))
         slots = [e.slot for e in entries]

@@ -113,6 +113,12 @@ def timers() -> Timers:
     return Timers()
 
 
+def timing() -> bool:
+    """Whether `timers()` is active: every launch is followed by an event then, so nothing may be captured
+    into a graph or replayed from one (a replay is opaque to the events)."""
+    return _timeline is not None
+
+
 def _mark(what):
     if _timeline is not None:
         ev = torch.cuda.Event(enable_timing=True)
