@@ -156,8 +156,16 @@ class Engine:
         """Captures the step that was just issued with `ctx` (whose plans, made on the host during that run,
         stay with it) for later steps of the same shape.  Nothing runs during the capture."""
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx, self.cache)
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.cache)
+        except Exception as e:       # noqa: BLE001 - the step itself has run and is committed; only the replay is lost
+            import warnings
+            warnings.warn(f"a prompt step could not be captured in a CUDA graph ({e}); steps are issued launch by "
+                          "launch from now on", RuntimeWarning, stacklevel=3)
+            self.prompt_graphs = False
+            self._graphs.clear()
+            return
         self._graphs[shape] = (ctx, graph, logits)
         while len(self._graphs) > self.PROMPT_GRAPHS_KEPT:
             self._graphs.popitem(last=False)
