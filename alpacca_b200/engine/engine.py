@@ -6,11 +6,13 @@ of unequal lengths go in one step; afterwards one token per sequence.  The
 reference's counterparts are `prefill` / `forward_batch` / `forward`
 (alpacca/model.py:610-641, :469-518, :439-445), for its single sequence.
 
-A prompt step whose shape was seen before (the same numbers of new and held tokens of every sequence,
-the same wanted places per sequence) is replayed from a CUDA graph: the second step of a shape is run
+A step whose shape was seen before is replayed from a CUDA graph: the second step of a shape is run
 launch by launch on index arrays that stay where they are and is captured afterwards, later ones copy
-their token ids, slots, pages and wanted places into those arrays and replay.  A step of 2,048 tokens
-of the 1B shape takes 3.8 ms of device time and 4.4 ms when the host issues its 130 launches one by one.
+their token ids, slots, pages and wanted places into those arrays and replay.  The shape of a prompt step
+is the numbers of new and held tokens of every sequence and of wanted places per sequence; of a step of
+one token each, the number of sequences and the width of the block tables (lengths are data there).  A
+step of 2,048 tokens of the 1B shape takes 3.8 ms of device time and 4.4 ms when the host issues its 130
+launches one by one; a step of one token 0.65 ms against about 2 ms.
 """
 from __future__ import annotations
 
@@ -43,8 +45,8 @@ class Engine:
                                    opts.dtype, self.device)
         self.vocab_size = model.spec.vocab_size
         self._builder = ContextBuilder(self.device)
-        # prompt steps replayed from graphs: shape -> times seen, shape -> (context, graph, logits)
-        self.prompt_graphs = self.device.type == "cuda" and model.all_capturable()
+        # steps replayed from graphs: shape -> times seen, shape -> (context, graph, logits)
+        self.step_graphs = self.device.type == "cuda" and model.all_capturable()
         self._shapes_seen: dict = {}
         self._graphs: OrderedDict = OrderedDict()
 
@@ -110,19 +112,26 @@ class Engine:
         return self._builder.build(entries, lengths, self.cache, arrays)
 
     PROMPT_GRAPH_MAX_TOKENS = 8192      # longer steps are bound by the device, not by the host that issues them
-    PROMPT_GRAPHS_KEPT = 8
+    STEP_GRAPHS_KEPT = 16
 
     def _shape_of(self, entries, lengths):
-        """What decides every launch of a prompt step (the rest - token ids, slots, pages, wanted places -
-        is data in device memory); None for steps that are not replayed from graphs."""
+        """(shape, block-table widths): what decides every launch of a step (the rest - token ids, slots,
+        pages, wanted places, and for single-token steps the lengths too - is data in device memory); the
+        shape is None for steps that are not replayed from graphs."""
         q_lens = tuple(len(e.tokens) for e in entries)
-        if (not self.prompt_graphs or max(q_lens) == 1 or sum(q_lens) > self.PROMPT_GRAPH_MAX_TOKENS
-                or ops.timing()):
-            return None
-        every = all(len(e.want) == q and all(w == i for i, w in enumerate(e.want)) for e, q in zip(entries, q_lens))
         slots = [e.slot for e in entries]
         widths = tuple(self.cache.table_width(g, slots) for g in range(len(self.cache.kv_groups)))
-        return q_lens, tuple(lengths), tuple(len(e.want) for e in entries), every, widths
+        if not self.step_graphs or sum(q_lens) > self.PROMPT_GRAPH_MAX_TOKENS or ops.timing():
+            return None, widths
+        wants = tuple(len(e.want) for e in entries)
+        every = all(len(e.want) == q and all(w == i for i, w in enumerate(e.want)) for e, q in zip(entries, q_lens))
+        if max(q_lens) == 1:
+            # one token each: the kernels take the lengths from device memory; tables as wide as the batch
+            # shapes of the graph decoder are, so that a shape lasts for many steps
+            from .decode import _width_bucket
+            widths = tuple(_width_bucket(w) for w in widths)
+            return ("one token each", len(entries), wants, every, widths), widths
+        return (q_lens, tuple(lengths), wants, every, widths), widths
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
         """Runs one step; returns float32 logits [number of wanted places, vocab] on the device,
@@ -131,17 +140,17 @@ class Engine:
         requests = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.reserve(requests)          # raises CacheFull before anything is launched
         lengths = [self.cache.length(e.slot) for e in entries]
-        shape = self._shape_of(entries, lengths)
+        shape, widths = self._shape_of(entries, lengths)
         held = self._graphs.get(shape) if shape is not None else None
         capture = None
         if held is not None:
             ctx, graph, logits = held
             self._graphs.move_to_end(shape)
-            self._builder.build(entries, lengths, self.cache, arrays, into=ctx.buffer)
+            self._builder.build(entries, lengths, self.cache, arrays, into=ctx.buffer, widths=widths)
             graph.replay()
             logits = logits.clone()           # the graph's own memory is written again by its next replay
         else:
-            ctx = self._builder.build(entries, lengths, self.cache, arrays)
+            ctx = self._builder.build(entries, lengths, self.cache, arrays, widths=widths)
             logits = self.model.forward(ctx, self.cache)
             if shape is not None:
                 seen = self._shapes_seen[shape] = self._shapes_seen.get(shape, 0) + 1
@@ -161,16 +170,22 @@ class Engine:
                 logits = self.model.forward(ctx, self.cache)
         except Exception as e:       # noqa: BLE001 - the step itself has run and is committed; only the replay is lost
             import warnings
-            warnings.warn(f"a prompt step could not be captured in a CUDA graph ({e}); steps are issued launch by "
+            warnings.warn(f"a step could not be captured in a CUDA graph ({e}); steps are issued launch by "
                           "launch from now on", RuntimeWarning, stacklevel=3)
-            self.prompt_graphs = False
+            self.step_graphs = False
             self._graphs.clear()
             return
         self._graphs[shape] = (ctx, graph, logits)
-        while len(self._graphs) > self.PROMPT_GRAPHS_KEPT:
+        while len(self._graphs) > self.STEP_GRAPHS_KEPT:
             self._graphs.popitem(last=False)
         if len(self._shapes_seen) > 4096:
             self._shapes_seen.clear()
+
+    def forget_graphs(self) -> None:
+        """Drops the captured steps: the next steps of every shape are issued launch by launch again (for a
+        caller that has changed what a step launches, such as a switch of `ops`)."""
+        self._graphs.clear()
+        self._shapes_seen.clear()
 
     def describe(self) -> str:
         return self.cache.describe()

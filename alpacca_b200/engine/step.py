@@ -75,15 +75,18 @@ class ContextBuilder:
         self._slot = i
         return buf
 
-    def build(self, entries, lengths, cache, token_arrays=None, into: torch.Tensor | None = None) -> StepContext:
+    def build(self, entries, lengths, cache, token_arrays=None, into: torch.Tensor | None = None,
+              widths=None) -> StepContext:
         """`into`: the `buffer` of a context built earlier for a step of the same shape (the same numbers of
         tokens, sequences, wanted places and pages): the arrays are written there instead of into new memory,
-        and nothing is returned (that context's views see them)."""
+        and nothing is returned (that context's views see them).  `widths`: the block tables' widths, one per
+        key/value group, if they are to be wider than the longest sequence needs (the rest is zero)."""
         B = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
         n_want = sum(len(e.want) for e in entries)
-        widths = [cache.table_width(g, [e.slot for e in entries]) for g in range(len(cache.kv_groups))]
+        if widths is None:
+            widths = [cache.table_width(g, [e.slot for e in entries]) for g in range(len(cache.kv_groups))]
         decode = all(q == 1 for q in q_lens)
         sizes = [T, T, T, B + 1, B, B, n_want] + [B * w for w in widths] + [B if decode else 0]
         offs = [0]

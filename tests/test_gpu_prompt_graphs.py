@@ -25,7 +25,7 @@ def test_steps_of_one_shape_with_other_tokens_slots_and_places(model_dirs, name,
     d = model_dirs[(name, dtype)]
     cfg = CONFIGS[name]
     eng = make_engine(d, dtype, max_tokens=64 * 30, max_slots=12)
-    assert eng.prompt_graphs
+    assert eng.step_graphs
     top = cfg["max_position_embeddings"]
     lens = [n for n in (70, 5, 33) if n <= top] + ([200] if top >= 512 else [])
     parked = []
@@ -88,7 +88,7 @@ def test_long_prompts_through_the_tensor_core_kernels(model_dirs):
     cfg = dict(CONFIGS["E"])
     eng = make_engine(d, "bfloat16", max_tokens=64 * 40, max_slots=4)
     ref = make_engine(d, "bfloat16", max_tokens=64 * 40, max_slots=4)
-    ref.prompt_graphs = False
+    ref.step_graphs = False
     for rnd in range(4):
         t = tiny.prompt_tokens(cfg, 500, 3000 + rnd)
         a, b = eng.alloc_slot(), ref.alloc_slot()
