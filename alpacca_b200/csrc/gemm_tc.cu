@@ -102,6 +102,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// g / (1 + e^-g) with the hardware's approximate exponential and division (relative error about 2^-21,
+// far below the bfloat16 rounding of the result): in the tail of a tile, where it runs beside the next
+// tile's MMAs, the exact forms cost 9 us of a 100 us product (2048 x 16384 x 2048), these 3.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
 template <int BN> struct TcShape {
   // few columns: the kernel streams weights and is bound by bytes in flight, so a deep ring;
   // many columns: bound by the tensor cores, and two CTAs per SM overlap tails with main loops
@@ -134,7 +139,7 @@ __device__ __forceinline__ void tail16(const float* v, int row_g, int col0_g, in
         for (int e = 0; e < 2; ++e) {
           const int u = 2 * j + e;
           const float g = v[u] + (bias ? bias[col0_g + u] : 0.f), up = v[8 + u] + (bias ? bias[col0_g + 8 + u] : 0.f);
-          a[e] = g / (1.0f + expf(-g)) * up;
+          a[e] = silu_fast(g) * up;
         }
         __nv_bfloat162 r = __floats2bfloat162_rn(a[0], a[1]);
         w[j] = *reinterpret_cast<uint32_t*>(&r);
@@ -176,7 +181,7 @@ __device__ __forceinline__ void tail16(const float* v, int row_g, int col0_g, in
         const float partner = __shfl_down_sync(0xffffffffu, mine, 8);
         const int m = col0_g + c;
         if (!(lane & 8) && n < rows_total && m < cols_total)
-          reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + unit] = __float2bfloat16_rn(mine / (1.0f + expf(-mine)) * partner);
+          reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + unit] = __float2bfloat16_rn(silu_fast(mine) * partner);
       }
     } else {
       if (n >= rows_total) return;
