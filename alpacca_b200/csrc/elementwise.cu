@@ -556,13 +556,18 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
                                       int* __restrict__ rng_step, const int* __restrict__ tok_seq,
                                       const int* __restrict__ sampled, int* __restrict__ recent,
                                       int* __restrict__ recent_pos, int window, int* __restrict__ history,
-                                      int* __restrict__ counter, int history_len, int n_rows) {
+                                      int* __restrict__ counter, int history_len, int* __restrict__ host_ring,
+                                      int ring_len, int n_rows) {
   pdl_wait();
   pdl_trigger();
   const int slot = history ? (*counter % history_len) : 0;
+  const int ring_slot = host_ring ? (*counter % ring_len) : 0;
   for (int b = threadIdx.x; b < n_rows; b += blockDim.x) {
     const int tok = sampled[b];
     if (history) history[(size_t)slot * n_rows + b] = tok;
+    // pinned host memory that the device can write: the host reads the step's tokens there once the step's
+    // event has passed (a copy after the graph costs a change of engines between every two replays)
+    if (host_ring) host_ring[(size_t)ring_slot * n_rows + b] = tok;
     if (tok_seq[b] < 0) continue;
     tokens[b] = tok;
     tok_pos[b] += 1;
@@ -580,9 +585,12 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
 
 AB_API int ab_decode_advance(int* tokens, int* tok_pos, int* kv_len, int* rng_step, const int* tok_seq,
                              const int* sampled, int* recent, int* recent_pos, int window, int* history,
-                             int* counter, int history_len, int n_rows, cudaStream_t stream) {
+                             int* counter, int history_len, int* host_ring, int ring_len, int n_rows,
+                             cudaStream_t stream) {
   if (n_rows <= 0) return AB_OK;
+  if (host_ring && (!counter || ring_len <= 0)) return AB_BAD_ARG;
   ab_launch(decode_advance_kernel, 1, 256, 0, stream, tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent,
-                                               recent_pos, window, history, counter, history_len, n_rows);
+                                               recent_pos, window, history, counter, history_len, host_ring, ring_len,
+                                               n_rows);
   return ab_launch_status();
 }

@@ -68,6 +68,7 @@ def _width_bucket(pages: int) -> int:
 
 class _Shape:
     """Static device buffers and the captured graph of one batch shape (rows, block-table width)."""
+    RING = 4        # more than the steps that are in flight at once
 
     def __init__(self, dec, rows: int, width: int):
         eng = dec.engine
@@ -92,7 +93,10 @@ class _Shape:
         o, n = self.sect["tok_seq"]
         self.mask_host, self.mask_dev = self.host[o:o + n], self.dev[o:o + n]   # the live mask of the rows
         self.sampled = torch.zeros(rows, dtype=torch.int32, device=dev)
-        self.sampled_hosts = [torch.zeros(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        # the tokens of the last steps, written by the step's last kernel itself into pinned host memory:
+        # row (number of the replay) % RING; `replayed` counts the replays as the device's counter does
+        self.host_ring = torch.zeros((self.RING, rows), dtype=torch.int32, pin_memory=True)
+        self.replayed = 0
         self.history = torch.zeros((dec.history_len, rows), dtype=torch.int32, device=dev)
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.graph = None
@@ -140,7 +144,6 @@ class GraphDecoder:
         self.pages_seen = -1
         self._last_slots, self._last_rows, self._room = None, None, 0
         self._flights: list = []        # steps that run ahead of the caller, oldest first
-        self._buf = 0
 
     # -- the captured step -------------------------------------------------------------
     def _body(self, sh: _Shape):
@@ -155,7 +158,7 @@ class GraphDecoder:
                    0, sh.d("rng_stream"), sh.d("rng_step"), seed_dev=sh.d("seed"))
         ops.decode_advance(sh.d("tokens"), sh.d("tok_pos"), sh.d("kv_len"), sh.d("rng_step"), sh.d("tok_seq"),
                            sh.sampled, recent, sh.d("recent_pos") if recent is not None else None, self.window,
-                           sh.history, sh.counter, sh.rows)
+                           sh.history, sh.counter, sh.rows, host_ring=sh.host_ring)
 
     def _capture(self, sh: _Shape):
         # with every row marked as padding the step touches neither cache nor counters, so the
@@ -176,6 +179,7 @@ class GraphDecoder:
             self._body(sh)
         sh.kernels = ops.launches - before      # kernels of this package in one replay
         sh.counter.zero_()
+        sh.replayed = 0
 
     # -- layout ----------------------------------------------------------------------------
     def _reserve(self, live, steps: int):
@@ -319,18 +323,18 @@ class GraphDecoder:
         rows = self._prepare(live, steps, always_mask)
         for _ in range(steps):
             self.shape.graph.replay()
+        self.shape.replayed += steps
         cache = self.engine.cache
         cache.commit([(slot, steps) for slot, _, _ in live])
         self.expect = {slot: (cache.length(slot), None) for slot, _, _ in live}
         return rows
 
     def _launch(self, live):
-        """Enqueues one step for `live` and the read-back of its tokens into a pinned buffer of its own."""
+        """Enqueues one step for `live`; its tokens arrive in a row of the shape's pinned ring (written by the
+        step's last kernel), to be read once the event recorded behind the step has passed."""
         rows = self.run(live, 1, always_mask=True)
         sh = self.shape
-        self._buf ^= 1
-        host = sh.sampled_hosts[self._buf]
-        host.copy_(sh.sampled, non_blocking=True)
+        host = sh.host_ring[(sh.replayed - 1) % sh.RING]      # where this replay's last kernel writes its tokens
         done = torch.cuda.Event()
         done.record()
         return {"live": list(live), "rows": rows, "done": done, "host": host}

@@ -772,8 +772,10 @@ def sample(logits, out, temperature, top_k, top_p, seed, streams, steps, seed_de
 
 
 def decode_advance(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, recent_pos, window,
-                   history, counter, n_rows):
-    """Feeds the sampled tokens back as the next step's inputs (all int32, on the device); see the kernel."""
+                   history, counter, n_rows, host_ring=None):
+    """Feeds the sampled tokens back as the next step's inputs (all int32, on the device); see the kernel.
+    `host_ring`: pinned host memory int32 [R, rows]; the step's tokens are also written to its row
+    counter % R, by the kernel itself."""
     _cuda(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, recent_pos, history, counter)
     for t, name in ((tokens, "tokens"), (tok_pos, "tok_pos"), (kv_len, "kv_len"), (rng_step, "rng_step"),
                     (tok_seq, "tok_seq"), (sampled, "sampled")):
@@ -787,9 +789,16 @@ def decode_advance(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, 
         _need(recent.dtype == torch.int32 and recent.is_contiguous() and recent.numel() >= n_rows * window
               and recent_pos is not None, "decode_advance: recent int32 [rows, window]")
         _i32(recent_pos, n_rows, "recent_pos")
+    ring_len = 0
+    if host_ring is not None:
+        _need(host_ring.device.type == "cpu" and host_ring.is_pinned() and host_ring.dtype == torch.int32
+              and host_ring.is_contiguous() and host_ring.dim() == 2 and host_ring.shape[1] == n_rows
+              and counter is not None, "decode_advance: host_ring pinned int32 [R, rows], with a counter")
+        ring_len = host_ring.shape[0]
     _check(_lib("elementwise").ab_decode_advance(
         _p(tokens), _p(tok_pos), _p(kv_len), _p(rng_step), _p(tok_seq), _p(sampled), _p(recent), _p(recent_pos),
-        int(window), _p(history), _p(counter), hist_len, n_rows, _stream()), "decode_advance")
+        int(window), _p(history), _p(counter), hist_len, _p(host_ring), ring_len, n_rows, _stream()),
+        "decode_advance")
 
 
 def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None, slices=None, persistent=True,
