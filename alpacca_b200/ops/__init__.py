@@ -413,6 +413,7 @@ def _prefill_tiles(ctx, G, device, rows=64):
 
 
 _ARRIVALS: dict = {}
+_OUTGROWN: list = []      # scratch that was replaced by larger scratch: kept, since graphs captured earlier use it
 DECODE_MAX_CLUSTER = 8           # chunks of one (sequence, head) that the decode attention merges in a cluster
 USE_TCGEN05_ATTENTION = True     # prefill steps of 128 tokens or more, head size 64: the tcgen05 kernel
 
@@ -426,6 +427,8 @@ def _arrival_counters(device, n: int):
         if torch.cuda.is_current_stream_capturing():
             raise KernelError(f"attention: {n} arrival counters needed during graph capture, "
                               f"{0 if buf is None else buf.numel()} allocated before it")
+        if buf is not None:
+            _OUTGROWN.append(buf)        # captured graphs may still point at it
         buf = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
         _ARRIVALS[device] = buf
     return buf
@@ -476,6 +479,8 @@ def _stream_scratch(device, n_partial: int, n_counters: int):
             raise KernelError(f"attention: scratch for {n_partial} partial sums needed during graph capture, "
                               f"{0 if have is None else have[0].numel()} allocated before it")
         n_partial = max(n_partial, 1 << 22)
+        if have is not None:
+            _OUTGROWN.append(have)       # captured graphs may still point at it
         have = (torch.empty(n_partial, dtype=torch.float32, device=device),
                 torch.empty(max(n_partial // 8, 1 << 16), dtype=torch.float32, device=device),
                 torch.zeros(max(n_counters, 1 << 16), dtype=torch.int32, device=device))
