@@ -97,14 +97,14 @@ __device__ __forceinline__ void attend_tile(RowState<DMAX>& st, const bf16* qs, 
   const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
   // a row that has seen no key yet keeps m = -inf; subtract 0 then, so that exp2(-inf - 0) = 0
   const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
-  const float corr0 = exp2f(st.m[0] - sub0), corr1 = exp2f(st.m[1] - sub1);
+  const float corr0 = fast_exp2(st.m[0] - sub0), corr1 = fast_exp2(st.m[1] - sub1);
   float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt) {
-    s[nt][0] = exp2f(s[nt][0] - sub0);
-    s[nt][1] = exp2f(s[nt][1] - sub0);
-    s[nt][2] = exp2f(s[nt][2] - sub1);
-    s[nt][3] = exp2f(s[nt][3] - sub1);
+    s[nt][0] = fast_exp2(s[nt][0] - sub0);
+    s[nt][1] = fast_exp2(s[nt][1] - sub0);
+    s[nt][2] = fast_exp2(s[nt][2] - sub1);
+    s[nt][3] = fast_exp2(s[nt][3] - sub1);
     sum0 += s[nt][0] + s[nt][1];
     sum1 += s[nt][2] + s[nt][3];
   }
@@ -329,14 +329,14 @@ __device__ __forceinline__ void attend_run(DecodeState<DMAX>& st, const uint32_t
   }
   const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
   const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
-  const float corr0 = exp2f(st.m[0] - sub0), corr1 = exp2f(st.m[1] - sub1);
+  const float corr0 = fast_exp2(st.m[0] - sub0), corr1 = fast_exp2(st.m[1] - sub1);
   float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
   for (int i = 0; i < DECODE_RUN; ++i) {
-    s[i][0] = exp2f(s[i][0] - sub0);
-    s[i][1] = exp2f(s[i][1] - sub1);
-    s[i][2] = exp2f(s[i][2] - sub0);
-    s[i][3] = exp2f(s[i][3] - sub1);
+    s[i][0] = fast_exp2(s[i][0] - sub0);
+    s[i][1] = fast_exp2(s[i][1] - sub1);
+    s[i][2] = fast_exp2(s[i][2] - sub0);
+    s[i][3] = fast_exp2(s[i][3] - sub1);
     sum0 += s[i][0] + s[i][2];
     sum1 += s[i][1] + s[i][3];
   }

@@ -109,7 +109,7 @@ __device__ __forceinline__ void attend_tile16(StreamState<HD>& st, const uint32_
   const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
   if (__any_sync(0xffffffffu, mn0 > st.m[0] || mn1 > st.m[1])) {
     // a maximum grew: bring the sums to the new reference (2^(-inf - x) = 0 clears an empty state)
-    const float c0 = (mn0 == -INFINITY) ? 1.f : exp2f(st.m[0] - mn0), c1 = (mn1 == -INFINITY) ? 1.f : exp2f(st.m[1] - mn1);
+    const float c0 = (mn0 == -INFINITY) ? 1.f : fast_exp2(st.m[0] - mn0), c1 = (mn1 == -INFINITY) ? 1.f : fast_exp2(st.m[1] - mn1);
     st.l[0] *= c0;
     st.l[1] *= c1;
 #pragma unroll
@@ -123,10 +123,10 @@ __device__ __forceinline__ void attend_tile16(StreamState<HD>& st, const uint32_
     st.m[1] = mn1;
   }
   const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
-  s[0] = exp2f(s[0] - sub0);
-  s[1] = exp2f(s[1] - sub1);
-  s[2] = exp2f(s[2] - sub0);
-  s[3] = exp2f(s[3] - sub1);
+  s[0] = fast_exp2(s[0] - sub0);
+  s[1] = fast_exp2(s[1] - sub1);
+  s[2] = fast_exp2(s[2] - sub0);
+  s[3] = fast_exp2(s[3] - sub1);
   st.l[0] += s[0] + s[2];
   st.l[1] += s[1] + s[3];
   // O^T += V^T P^T; P^T as the second operand is the transposed accumulator of S^T
