@@ -23,6 +23,12 @@ class KernelError(RuntimeError):
     pass
 
 
+# The library products of this package (`torch.mm` on bfloat16 operands) add in float32 throughout: the
+# library may not reduce partial sums of a split inner dimension in bfloat16 (measured on a B200 at the 1B
+# sizes: the same step times and the same results either way; the setting makes it a rule).
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+
 def _lib(name):
     return build.load(name)
 
